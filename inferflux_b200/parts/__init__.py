@@ -1,9 +1,9 @@
 """The parts layers are made of.  Importing the package registers the built-in kinds."""
 from .base import (Block, FeedForward, KVCacheSpec, Mixer, Norm, NormedDelta, Part, PositionEncoding, RotaryTable,
-                   StateSpec, StreamMerge, TimeConv, WeightBuffers, build_part, register_part, registered_parts,
+                   StateSpec, StreamMerge, TimeConv, TokenInput, WeightBuffers, build_part, register_part, registered_parts,
                    settle_pending)
-from . import attention, block, conv, embedding, latent_attention, mlp, moe, norm, rope, wkv  # noqa: F401  (registration)
+from . import attention, block, conv, delta_rule, embedding, latent_attention, mlp, moe, norm, rope, token_input, wkv  # noqa: F401  (registration)
 
 __all__ = ["Block", "FeedForward", "KVCacheSpec", "Mixer", "Norm", "NormedDelta", "Part", "PositionEncoding",
-           "RotaryTable", "StateSpec", "StreamMerge", "TimeConv", "WeightBuffers", "build_part", "register_part",
+           "RotaryTable", "StateSpec", "StreamMerge", "TimeConv", "TokenInput", "WeightBuffers", "build_part", "register_part",
            "registered_parts", "settle_pending"]

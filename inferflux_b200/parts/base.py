@@ -11,6 +11,7 @@ does its work through the kernel table of the step (`ctx.kernels`).
     FeedForward       forward(h, ctx) -> y
     TimeConv          state_rows; forward(h, ctx, state, index) -> h'
     StreamMerge       forward(x, x0, repeat, ctx) -> x'
+    TokenInput        forward(x, ctx) -> delta
     Block             sub_parts (name -> role); forward(x, pending, ctx, cache) -> (x, pending)
 
 `x` is the float32 residual stream [tokens, hidden]; `h` and `y` are in the dtype
@@ -83,6 +84,7 @@ class RotaryTable:
     inv_freq: torch.Tensor
     rotary_dim: int
     interleaved: bool            # False: (i, i + rotary_dim/2); True: (2i, 2i+1)
+    magnitude: float = 1.0       # cos and sin are multiplied by this
 
 
 # ------------------------------------------------------------------ weight storage
@@ -197,6 +199,14 @@ class TimeConv(Part):
         raise NotImplementedError
 
 
+class TokenInput(Part):
+    """Something a layer adds to the residual stream from the step's token ids and the stream itself."""
+
+    def forward(self, x: torch.Tensor, ctx):
+        """`x`: the float32 residual stream [T, hidden], read only.  Returns the delta, plain or a `NormedDelta`."""
+        raise NotImplementedError
+
+
 class StreamMerge(Part):
     """Makes a new residual stream from the present one and the embedding output."""
 
@@ -234,7 +244,7 @@ class Block(Part):
 
 _REGISTRIES: Dict[str, Dict[str, type]] = {
     "mixer": {}, "ffn": {}, "norm": {}, "position": {}, "block": {}, "embedding": {}, "lm_head": {},
-    "conv": {}, "merge": {},
+    "conv": {}, "merge": {}, "token_input": {},
 }
 
 

@@ -4,6 +4,7 @@ delta on unadded, so that whatever normalises next adds it in the same kernel
 (runtime/backends/cuda/native/transformer_forward.cu:2203-2211, 2564-2586)."""
 from __future__ import annotations
 
+import dataclasses
 from typing import Optional
 
 import torch
@@ -155,6 +156,84 @@ class PostNormBlock(Block):
         h = self._sublayer_input(x, pending, self.ffn, ctx)
         y = self.ffn.forward(h, ctx)
         return x, NormedDelta(y, self.postnorm_ffn.weight, self.postnorm_ffn.eps)
+
+
+@register_part("block", "parallel")
+class ParallelBlock(Block):
+    """One norm that both sublayers read, their outputs added together, then optionally a token input:
+
+        h = norm(x);   x += m * (mixer(h + conv(h)) + ffn(h));   x += side(x)
+
+    params: ffn, conv, side (whether the layer has each; defaults True, False, False), residual_mult (m, default 1).
+    Parts, as far as present: norm, conv, mixer, ffn, side.  The convolution's inputs of the last few tokens and
+    the mixer's own state share the layer's state row per request: [convolution rows, then the mixer's].  What the
+    token input returns travels unadded (`pending`), so that its sum, its norm and the next layer's norm are one
+    kernel; in steps of single tokens that kernel does the convolution too and hands back both h and h + conv(h)."""
+
+    def __init__(self, spec, parts):
+        self.has_ffn = bool(spec.params.get("ffn", True))
+        self.has_conv = bool(spec.params.get("conv", False))
+        self.has_side = bool(spec.params.get("side", False))
+        self.mult = float(spec.params.get("residual_mult", 1.0))
+        names = {"norm": "norm", "mixer": "mixer"}
+        if self.has_ffn:
+            names["ffn"] = "ffn"
+        if self.has_conv:
+            names["conv"] = "conv"
+        if self.has_side:
+            names["side"] = "token_input"
+        self.sub_parts = names
+        super().__init__(spec, parts)
+        if not isinstance(self.norm, RMSNorm):
+            raise ValueError("parallel block: norm must be an RMS norm (its weight and eps go into a fused kernel)")
+        conv = parts.get("conv")
+        self.conv_floats = (conv.state_rows or 0) * conv.channels if conv is not None else 0
+
+    def cache_part(self):
+        own = self.mixer.state_spec()
+        if own is not None and own.dtype != torch.float32:
+            raise ValueError("parallel block: the mixer's state must be float32 to share the layer's state row")
+        if not self.conv_floats:
+            return self.mixer
+        size = 1
+        for d in (own.shape if own is not None else (0,)):
+            size *= int(d)
+        return _StoresForBlock(self.mixer, StateSpec((self.conv_floats + (size if own is not None else 0),), torch.float32))
+
+    def _views(self, cache):
+        """(the convolution's state [slots, 1, rows, width], the cache as the mixer sees it)."""
+        if not self.conv_floats or cache.state is None:
+            return None, cache
+        conv = self.conv
+        conv_state = cache.state[:, :self.conv_floats].unflatten(1, (1, conv.state_rows, conv.channels))
+        rest = cache.state[:, self.conv_floats:] if cache.state.shape[1] > self.conv_floats else None
+        return conv_state, dataclasses.replace(cache, state=rest)
+
+    def forward(self, x, pending, ctx, cache):
+        k = ctx.kernels
+        conv = self.parts.get("conv")
+        conv_state, mixer_cache = self._views(cache)
+        norm = self.norm
+        hc = None
+        if isinstance(pending, NormedDelta):
+            if conv is not None and ctx.max_span == 1 and getattr(k, "fuses_single_token_conv", False):
+                # decoded tokens only: sum, both norms and the convolution (its history is all state) in one kernel
+                h, hc = k.postnorm_add(x, pending.y, pending.weight, pending.eps, norm.weight, norm.eps, ctx.dtype,
+                                       conv=(conv.weight, conv.taps, conv_state, 0, ctx), groups=norm.groups, both=True)
+            else:
+                h = k.postnorm_add(x, pending.y, pending.weight, pending.eps, norm.weight, norm.eps, ctx.dtype,
+                                   groups=norm.groups)
+        else:
+            h = norm.forward(x, pending, ctx)
+        if hc is None:
+            hc = conv.forward(h, ctx, conv_state, 0) if conv is not None else h
+        y = self.mixer.forward(hc, ctx, mixer_cache)
+        f = self.ffn.forward(h, ctx) if self.has_ffn else None
+        if not self.has_side:
+            k.residual_add_scaled(x, y, f, self.mult)
+            return x, None
+        rows = k.residual_add_scaled(x, y, f, self.mult, out_dtype=ctx.dtype)      # x in the run's dtype, for the gate
+        return x, self.side.forward(x, ctx, rows=rows)
 
 
 @register_part("merge", "linear_reinject")

@@ -18,7 +18,9 @@ from .base import Part, register_part
 @register_part("embedding", "embedding")
 class Embedding(Part):
     """params: vocab_size, hidden_size, tensor_name (default `weight`), norm (None, or {tensor_name, eps}:
-    the gathered rows are RMS-normed with that weight, in float32, before they become the residual stream)."""
+    the gathered rows are RMS-normed with that weight, in float32, before they become the residual stream),
+    scale (default 1: the gathered rows are multiplied by it, in float32), side_table (None, or {tensor_name, width}:
+    a second table [vocab, width] whose rows layers read by token id; a step finds it in `ctx.side_table`)."""
 
     def __init__(self, spec):
         super().__init__(spec)
@@ -28,10 +30,16 @@ class Embedding(Part):
         norm = spec.params.get("norm")
         self.norm_name = None if not norm else str(norm.get("tensor_name", "norm.weight"))
         self.norm_eps = float(norm["eps"]) if norm else 0.0
-        self.table = self.norm_weight = None
+        self.scale = float(spec.params.get("scale", 1.0))
+        side = spec.params.get("side_table")
+        self.side_name = None if not side else str(side["tensor_name"])
+        self.side_width = int(side["width"]) if side else 0
+        self.table = self.norm_weight = self.side_table = None
 
     def param_specs(self):
         specs = {self.tensor_name: TensorSpec((self.vocab, self.hidden))}
+        if self.side_name is not None:
+            specs[self.side_name] = TensorSpec((self.vocab, self.side_width))
         if self.norm_name is not None:
             specs[self.norm_name] = TensorSpec((self.hidden,), init="ones")
         return specs
@@ -40,9 +48,15 @@ class Embedding(Part):
         self.table = tensors[self.tensor_name].to(device=device, dtype=dtype).contiguous()
         if self.norm_name is not None:
             self.norm_weight = tensors[self.norm_name].to(device=device, dtype=torch.float32).contiguous()
+        if self.side_name is not None:
+            self.side_table = tensors[self.side_name].to(device=device, dtype=dtype).contiguous()
 
     def forward(self, ctx):
-        x = ctx.kernels.embed(self.table, ctx.token_ids, self.vocab)
+        ctx.side_table = self.side_table
+        if self.scale != 1.0:
+            x = ctx.kernels.embed(self.table, ctx.token_ids, self.vocab, scale=self.scale)
+        else:
+            x = ctx.kernels.embed(self.table, ctx.token_ids, self.vocab)
         if self.norm_weight is not None:
             x = ctx.kernels.rmsnorm(x, self.norm_weight, self.norm_eps, torch.float32)
         return x
@@ -51,7 +65,7 @@ class Embedding(Part):
 @register_part("lm_head", "lm_head")
 class LMHead(Part):
     """params: vocab_size, hidden_size, tied, softcap (None, or c: logits become c tanh(logits / c)),
-    tensor_name (default `weight`)."""
+    scale (default 1: the float32 logits are multiplied by it), tensor_name (default `weight`)."""
 
     def __init__(self, spec):
         super().__init__(spec)
@@ -62,6 +76,7 @@ class LMHead(Part):
         self.softcap = None if cap is None else float(cap)
         if self.softcap is not None and not self.softcap > 0:
             raise ValueError(f"lm_head: softcap must be positive, got {self.softcap}")
+        self.scale = float(spec.params.get("scale", 1.0))
         self.tensor_name = str(spec.params.get("tensor_name", "weight"))
         self.weight = None
 
@@ -79,6 +94,8 @@ class LMHead(Part):
     def forward(self, h, ctx):
         """h: normed rows [R, hidden] -> float32 logits [R, vocab]."""
         logits = ctx.kernels.linear(h, self.weight, out_dtype=torch.float32)
+        if self.scale != 1.0:
+            ctx.kernels.scale_(logits, self.scale)
         if self.softcap is not None:
             ctx.kernels.softcap(logits, self.softcap)
         return logits

@@ -7,6 +7,11 @@
 An expert is W_down act(W_up h) with act = relu^2 and no biases.  The last `identity` router outputs have no
 weights: such an expert hands h on unchanged.  Expert weights are stacked at load, [experts, ff, width] and
 [experts, width, ff], so that the kernels find an expert by its number.
+
+Options.  `routing` = `softmax_of_chosen`: the `top` largest logits are chosen and the weights are the softmax over
+those alone.  `activation` = `clamped_glu`: an expert has a gate matrix too (stacked as [experts, 2 ff, width], an
+expert's gate rows above its up rows) and, with g = min(W_gate h, limit) and u = clamp(W_up h, -limit, limit),
+makes W_down (g sigmoid(1.702 g) (u + 1)).
 """
 from __future__ import annotations
 
@@ -19,10 +24,12 @@ from .base import FeedForward, WeightBuffers, register_part
 @register_part("ffn", "moe")
 class MixtureOfExperts(FeedForward):
     """params: hidden_size, expert_size (ff of an expert), num_experts, num_identity (default 0), top,
-    activation (`relu2`), correction (whether a selection bias tensor exists; default True),
-    names (tensor names of router, correction, and the patterns `up` / `down` with {e} for the expert's number)."""
+    activation (`relu2` or `clamped_glu` with `limit`), routing (`softmax_of_all`, the default, or
+    `softmax_of_chosen`), correction (whether a selection bias tensor exists; default True),
+    names (tensor names of router, correction, and the patterns `gate` / `up` / `down` with {e} for the expert's number)."""
 
-    _NAMES = {"router": "router", "correction": "correction", "up": "e{e}.up", "down": "e{e}.down"}
+    _NAMES = {"router": "router", "correction": "correction", "up": "e{e}.up", "down": "e{e}.down", "gate": "e{e}.gate"}
+    GLU_SLOPE = 1.702                 # the sigmoid's slope in the gated activation
 
     def __init__(self, spec):
         super().__init__(spec)
@@ -33,8 +40,15 @@ class MixtureOfExperts(FeedForward):
         self.identity = int(p.get("num_identity", 0))
         self.top = int(p["top"])
         self.activation = str(p.get("activation", "relu2"))
-        if self.activation != "relu2":
-            raise ValueError(f"moe: unknown activation {self.activation!r} (known: relu2)")
+        if self.activation not in ("relu2", "clamped_glu"):
+            raise ValueError(f"moe: unknown activation {self.activation!r} (known: relu2, clamped_glu)")
+        self.gated = self.activation == "clamped_glu"
+        self.limit = float(p["limit"]) if self.gated else 0.0
+        if self.gated and not self.limit > 0:
+            raise ValueError(f"moe: the gated activation's limit must be positive, got {self.limit}")
+        self.routing = str(p.get("routing", "softmax_of_all"))
+        if self.routing not in ("softmax_of_all", "softmax_of_chosen"):
+            raise ValueError(f"moe: unknown routing {self.routing!r}")
         if self.experts < 0 or self.identity < 0 or self.experts + self.identity < 1:
             raise ValueError("moe: there must be at least one expert")
         if not 1 <= self.top <= self.experts + self.identity:
@@ -52,6 +66,8 @@ class MixtureOfExperts(FeedForward):
         if self.has_correction:
             specs[n["correction"]] = TensorSpec((outs,), init="zeros")
         for e in range(self.experts):
+            if self.gated:
+                specs[n["gate"].format(e=e)] = TensorSpec((self.ff, self.hidden))
             specs[n["up"].format(e=e)] = TensorSpec((self.ff, self.hidden))
             specs[n["down"].format(e=e)] = TensorSpec((self.hidden, self.ff))
         return specs
@@ -60,7 +76,7 @@ class MixtureOfExperts(FeedForward):
         n, outs = self.names, self.experts + self.identity
         layout = {"router": ((outs, self.hidden), dtype), "correction": ((outs,), torch.float32)}
         if self.experts:
-            layout["up"] = ((self.experts, self.ff, self.hidden), dtype)
+            layout["up"] = ((self.experts, (2 if self.gated else 1) * self.ff, self.hidden), dtype)
             layout["down"] = ((self.experts, self.hidden, self.ff), dtype)
         self.buffers = buf = WeightBuffers(device, layout)
         buf["router"].copy_(tensors[n["router"]])
@@ -69,7 +85,11 @@ class MixtureOfExperts(FeedForward):
         else:
             buf["correction"].zero_()
         for e in range(self.experts):                    # each expert into its slice of the stack
-            buf["up"][e].copy_(tensors[n["up"].format(e=e)])
+            if self.gated:
+                buf["up"][e][:self.ff].copy_(tensors[n["gate"].format(e=e)])
+                buf["up"][e][self.ff:].copy_(tensors[n["up"].format(e=e)])
+            else:
+                buf["up"][e].copy_(tensors[n["up"].format(e=e)])
             buf["down"][e].copy_(tensors[n["down"].format(e=e)])
         self.w_router, self.correction = buf["router"], buf["correction"]
         self.w_up = buf["up"] if self.experts else None
@@ -78,5 +98,10 @@ class MixtureOfExperts(FeedForward):
     def forward(self, h, ctx):
         k = ctx.kernels
         z = k.linear(h, self.w_router, out_dtype=torch.float32)                   # [T, experts + identity]
+        if self.routing == "softmax_of_chosen" or self.gated:
+            ids, weights = k.moe_route(z, self.correction if self.has_correction else None, self.top,
+                                       of_chosen=self.routing == "softmax_of_chosen")
+            return k.moe_experts(h, self.w_up, self.w_down, ids, weights, self.experts, ctx.dtype,
+                                 glu=(self.limit, self.GLU_SLOPE) if self.gated else None)
         ids, weights = k.moe_route(z, self.correction, self.top)
         return k.moe_experts(h, self.w_up, self.w_down, ids, weights, self.experts, ctx.dtype)

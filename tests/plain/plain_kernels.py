@@ -21,13 +21,34 @@ class PlainKernels:
         self.launches = 0
 
     # ------------------------------------------------------------- elementwise
-    def embed(self, table, token_ids, vocab):
-        return table[token_ids.long()].to(torch.float32)
+    def embed(self, table, token_ids, vocab, scale=1.0):
+        return (table[token_ids.long()].to(self.acc) * scale).to(torch.float32)
 
-    def rmsnorm(self, x, w, eps, out_dtype):
+    def rmsnorm(self, x, w, eps, out_dtype, groups=1):
         xa = x.to(self.acc)
-        y = xa * torch.rsqrt((xa * xa).mean(-1, keepdim=True) + eps) * w.to(self.acc)
+        parts = xa.reshape(*xa.shape[:-1], groups, xa.shape[-1] // groups)
+        y = (parts * torch.rsqrt((parts * parts).mean(-1, keepdim=True) + eps)).reshape(xa.shape) * w.to(self.acc)
         return y.to(out_dtype)
+
+    def rmsnorm_columns(self, rows, col0, n, w, eps):
+        """Columns col0 .. col0 + n of `rows`, RMS-normed with weight `w`, as a tensor of their own."""
+        return self.rmsnorm(rows[:, col0:col0 + n], w, eps, rows.dtype)
+
+    def residual_add_scaled(self, x, a, b, scale, out_dtype=None):
+        """x += scale * (a + b) (b may be None); with `out_dtype` also returns the updated rows in that dtype."""
+        total = a.to(self.acc) if b is None else a.to(self.acc) + b.to(self.acc)
+        x += (scale * total).to(torch.float32)
+        return None if out_dtype is None else x.to(out_dtype)
+
+    def scale_(self, values, factor):
+        values.mul_(factor)
+
+    def gelu_mul_table(self, z, table, token_ids, first_column):
+        """gelu_tanh(z) * table[token, first_column : first_column + z.shape[1]] in z's dtype."""
+        za = z.to(self.acc)
+        e = table[token_ids.long()][:, first_column:first_column + z.shape[1]].to(self.acc)
+        g = 0.5 * za * (1.0 + torch.tanh(math.sqrt(2.0 / math.pi) * (za + 0.044715 * za ** 3)))
+        return (g * e).to(z.dtype)
 
     def add_rmsnorm(self, x, delta, w, eps, out_dtype):
         x += delta.to(torch.float32)
@@ -186,12 +207,12 @@ class PlainKernels:
         return out.reshape(T, nq * d)
 
     # ------------------------------------------- layers that norm a sublayer's output
-    def postnorm_add(self, x, y, w_post, eps_post, w_next=None, eps_next=0.0, out_dtype=None, cast_out=False):
+    def postnorm_add(self, x, y, w_post, eps_post, w_next=None, eps_next=0.0, out_dtype=None, cast_out=False, groups=1):
         ya = y.to(self.acc)
         x += (ya * torch.rsqrt((ya * ya).mean(-1, keepdim=True) + eps_post) * w_post.to(self.acc)).to(torch.float32)
         if w_next is None:
             return x.to(out_dtype or y.dtype) if cast_out else None
-        return self.rmsnorm(x, w_next, eps_next, out_dtype or y.dtype)
+        return self.rmsnorm(x, w_next, eps_next, out_dtype or y.dtype, groups=groups)
 
     def concat_cast(self, a, b, dtype):
         return torch.cat([a, b], dim=-1).to(dtype)
@@ -262,20 +283,54 @@ class PlainKernels:
         y = out.reshape(T, heads * dim) * norm_w.to(A) * (ga / (1.0 + torch.exp(-ga)))
         return y.to(out_dtype)
 
+    def delta_rule_scan(self, proj, w_raw, w0, a_bias, norm_w, eps, heads, dim, state, ctx, out_dtype):
+        """`proj`: float32 [T, 5 heads dim], the projections r, k, v, g, a side by side; `state`: float32 [slots, >= heads
+        dim dim] (rows may be further apart than that), the matrices S [head, key channel, value channel], moved on."""
+        T, A, HD = proj.shape[0], self.acc, heads * dim
+        shape = (T, heads, dim)
+        r, k, v, g, a = (proj[:, i * HD:(i + 1) * HD].to(A) for i in range(5))
+        r, k, v = r.view(shape), k.view(shape), v.view(shape)
+        decay = torch.exp(-math.exp(-0.5) * torch.sigmoid(w_raw.to(A) + w0.to(A))).view(shape)
+        erase = torch.sigmoid(a + a_bias.to(A)).view(shape)
+        unit = k / torch.sqrt((k * k).sum(-1, keepdim=True) + 1e-6)
+        out = torch.empty(shape, dtype=A)
+        cu, slots = ctx.cu_seqlens.tolist(), ctx.req_slot.tolist()
+        for q in range(ctx.num_requests):
+            S = state[slots[q], :HD * dim].to(A).view(heads, dim, dim).clone()
+            for t in range(cu[q], cu[q + 1]):
+                along = torch.einsum("hi,hij->hj", unit[t], S)
+                S = decay[t][:, :, None] * S - (erase[t] * unit[t])[:, :, None] * along[:, None, :] + k[t][:, :, None] * v[t][:, None, :]
+                out[t] = torch.einsum("hij,hi->hj", S, r[t])
+            state[slots[q], :HD * dim] = S.reshape(-1).to(state.dtype)
+        out = out * torch.rsqrt((out * out).mean(-1, keepdim=True) + eps)
+        return (out.reshape(T, HD) * norm_w.to(A) * torch.sigmoid(g)).to(out_dtype)
+
     # ------------------------------------------------------- mixture of experts
-    def moe_route(self, z, correction, top):
+    def moe_route(self, z, correction, top, of_chosen=False):
+        if of_chosen:                                       # the largest logits; softmax among them alone
+            za = z.to(self.acc) if correction is None else z.to(self.acc) + correction.to(self.acc)
+            best = torch.topk(za, top, dim=-1)
+            return best.indices.to(torch.int32), torch.softmax(torch.gather(z.to(self.acc), 1, best.indices), dim=-1).to(torch.float32)
         s = torch.softmax(z.to(self.acc), dim=-1)
         choice = s if correction is None else s + correction.to(self.acc)
         ids = torch.topk(choice, top, dim=-1).indices
         return ids.to(torch.int32), torch.gather(s, 1, ids).to(torch.float32)
 
-    def moe_experts(self, h, w_up, w_down, ids, weights, experts, out_dtype):
+    def moe_experts(self, h, w_up, w_down, ids, weights, experts, out_dtype, glu=None):
+        """`glu` = (limit, slope): w_up holds an expert's gate rows above its up rows, and the activation is
+        g sigmoid(slope g) (u + 1) with g = min(gate, limit), u = clamp(up, -limit, limit)."""
         ha = h.to(self.acc)
         out = torch.zeros_like(ha)
         for t in range(h.shape[0]):
             for e, wgt in zip(ids[t].tolist(), weights[t].to(self.acc)):
                 if e >= experts:
                     out[t] += wgt * ha[t]
+                elif glu is not None:
+                    both = w_up[e].to(self.acc) @ ha[t]
+                    ff = both.shape[0] // 2
+                    gate, up = torch.clamp(both[:ff], max=glu[0]), torch.clamp(both[ff:], min=-glu[0], max=glu[0])
+                    a = gate * torch.sigmoid(glu[1] * gate) * (up + 1.0)
+                    out[t] += wgt * (w_down[e].to(self.acc) @ a.to(h.dtype).to(self.acc))
                 else:
                     a = torch.relu(w_up[e].to(self.acc) @ ha[t]) ** 2
                     out[t] += wgt * (w_down[e].to(self.acc) @ a.to(h.dtype).to(self.acc))
@@ -291,7 +346,43 @@ class PlainKernels:
             page = cache.block_table[slot, pos // P].long()
             cache.kv[page, 0, 0, pos % P, :] = c.to(cache.kv.dtype)
 
-    def latent_attention(self, q_rows, w_uk, w_uv, sinks, heads, dim, vdim, rank, window, scale, ctx, cache):
+    def latent_rope_append(self, rows, col0, rank, rot, w, eps, q, heads, dim, rotary, ctx, cache):
+        """The cached row of every token: [columns col0 .. + rank of `rows`, RMS-normed with `w`; the `rot` columns
+        behind them, turned by the token's position].  Returns `q` [T, heads (dim + rot)] with every head's last `rot`
+        elements turned the same way (q itself may be changed)."""
+        A = self.acc
+        xa = rows[:, col0:col0 + rank].to(A)
+        c = xa * torch.rsqrt((xa * xa).mean(-1, keepdim=True) + eps) * w.to(A)
+        T = rows.shape[0]
+        pos = ctx.positions.to(A)
+
+        def turn(x):                                         # x: [T, n, rot]
+            if not rot or rotary is None:
+                return x
+            half = rotary.rotary_dim // 2
+            ang = pos[:, None] * rotary.inv_freq.to(A)[None, :]
+            cos, sin = (torch.cos(ang) * rotary.magnitude)[:, None, :], (torch.sin(ang) * rotary.magnitude)[:, None, :]
+            out = x.clone()
+            if rotary.interleaved:
+                u, v = x[..., 0:2 * half:2], x[..., 1:2 * half:2]
+                out[..., 0:2 * half:2], out[..., 1:2 * half:2] = u * cos - v * sin, v * cos + u * sin
+            else:
+                u, v = x[..., :half], x[..., half:2 * half]
+                out[..., :half], out[..., half:2 * half] = u * cos - v * sin, v * cos + u * sin
+            return out
+        kt = turn(rows[:, None, col0 + rank:col0 + rank + rot].to(A))[:, 0]
+        if cache.writes:
+            P, p = cache.page_size, ctx.positions.long()
+            slot = ctx.req_slot.long()[ctx.token_req.long()]
+            page = cache.block_table[slot, p // P].long()
+            cache.kv[page, 0, 0, p % P, :] = torch.cat([c, kt], dim=-1).to(cache.kv.dtype)
+        qa = q[:, :heads * (dim + rot)].to(A).reshape(T, heads, dim + rot).clone()
+        qa[:, :, dim:] = turn(qa[:, :, dim:])
+        return qa.reshape(T, heads * (dim + rot)).to(q.dtype)
+
+    def latent_attention(self, q_rows, w_uk, w_uv, sinks, heads, dim, vdim, rank, window, scale, ctx, cache, rot=0):
+        if rot:
+            return self._latent_attention_rot(q_rows, w_uk, w_uv, sinks, heads, dim, vdim, rank, window, scale, ctx, cache, rot)
         T, P = q_rows.shape[0], cache.page_size
         q = q_rows[:, :heads * dim].to(self.acc).view(T, heads, dim)
         uk, uv = w_uk.to(self.acc).view(heads, dim, rank), w_uv.to(self.acc).view(heads, vdim, rank)
@@ -305,6 +396,28 @@ class PlainKernels:
             C = cache.kv[pages, 0, 0, keys % P, :].to(self.acc)            # [n, rank]
             for h in range(heads):
                 s = (C @ (uk[h].t() @ q[t, h])) * scale
+                if sinks is not None:
+                    s = torch.cat([s, sinks[h:h + 1].to(self.acc)])
+                p = torch.softmax(s, dim=0)[:keys.numel()]
+                out[t, h] = (uv[h] @ (p @ C)).to(q_rows.dtype)
+        return out.reshape(T, heads * vdim)
+
+    def _latent_attention_rot(self, q_rows, w_uk, w_uv, sinks, heads, dim, vdim, rank, window, scale, ctx, cache, rot):
+        """Cached rows are [latent; turned key part]; a query head is [dim plain; rot turned] elements."""
+        T, P = q_rows.shape[0], cache.page_size
+        q = q_rows[:, :heads * (dim + rot)].to(self.acc).view(T, heads, dim + rot)
+        uk, uv = w_uk.to(self.acc).view(heads, dim, rank), w_uv.to(self.acc).view(heads, vdim, rank)
+        out = torch.empty((T, heads, vdim), dtype=q_rows.dtype, device=q_rows.device)
+        pos_all, req_all, slots = ctx.positions.tolist(), ctx.token_req.tolist(), ctx.req_slot.tolist()
+        for t in range(T):
+            pos, slot = pos_all[t], slots[req_all[t]]
+            first = max(0, pos - window + 1) if window else 0
+            keys = torch.arange(first, pos + 1, device=q_rows.device)
+            pages = cache.block_table[slot, keys // P].long()
+            rows = cache.kv[pages, 0, 0, keys % P, :].to(self.acc)         # [n, rank + rot]
+            C, Kt = rows[:, :rank], rows[:, rank:]
+            for h in range(heads):
+                s = (C @ (uk[h].t() @ q[t, h, :dim]) + Kt @ q[t, h, dim:]) * scale
                 if sinks is not None:
                     s = torch.cat([s, sinks[h:h + 1].to(self.acc)])
                 p = torch.softmax(s, dim=0)[:keys.numel()]
