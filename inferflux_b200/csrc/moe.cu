@@ -2,8 +2,12 @@
 //
 //   moe_route     scores = softmax(z) over all router outputs (float32); the `top` largest of score + correction
 //                 are chosen (the earlier index wins a tie); their weights are the scores themselves
+//                 (of_chosen: the `top` largest of z + correction are chosen and the weights are the softmax over
+//                 the chosen z alone)
 //   moe_up        act[p] = relu(W_up[e] h[t])^2 for every (token, choice) pair p = t * top + c whose expert e
-//                 has weights (experts numbered from `experts` on hand their input on unchanged)
+//                 has weights (experts numbered from `experts` on hand their input on unchanged); or, gated (an
+//                 expert's gate rows above its up rows, [experts, 2 ff, width]), with g = min(gate, limit) and
+//                 u = clamp(up, -limit, limit): act[p] = g sigmoid(slope g) (u + 1)
 //   moe_down      out[t] = sum over the token's choices, in their order, of weight * (W_down[e] act[p]), or
 //                 weight * h[t] for an expert without weights
 //
@@ -26,13 +30,52 @@ namespace ifx {
 constexpr int kMaxRouterOutputs = 1024;
 
 __global__ void moe_route_kernel(const float* __restrict__ z, const float* __restrict__ correction,
-                                 int* __restrict__ ids, float* __restrict__ weights, int T, int n, int top) {
+                                 int* __restrict__ ids, float* __restrict__ weights, int T, int n, int top, int of_chosen) {
   __shared__ float score_s[4][kMaxRouterOutputs];
   __shared__ float choice_s[4][kMaxRouterOutputs];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int t = blockIdx.x * 4 + warp;
   if (t >= T) return;
   const float* zr = z + (size_t)t * n;
+  if (of_chosen) {
+    for (int i = lane; i < n; i += 32) {
+      score_s[warp][i] = zr[i];
+      choice_s[warp][i] = zr[i] + (correction ? correction[i] : 0.0f);
+    }
+    __syncwarp();
+    float m = -INFINITY;                                // the largest chosen logit, known to lane 0
+    for (int c = 0; c < top; ++c) {
+      float best = -INFINITY;
+      int at = 0x7fffffff;
+      for (int i = lane; i < n; i += 32) {
+        const float v = choice_s[warp][i];
+        if (v > best) { best = v; at = i; }
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oa = __shfl_xor_sync(0xffffffffu, at, o);
+        if (ob > best || (ob == best && oa < at)) { best = ob; at = oa; }
+      }
+      if (at >= n) at = 0;
+      if (lane == 0) {
+        ids[(size_t)t * top + c] = at;
+        m = fmaxf(m, score_s[warp][at]);
+        choice_s[warp][at] = -INFINITY;
+      }
+      __syncwarp();
+    }
+    if (lane == 0) {                                     // softmax over the chosen alone, in the order of the choice
+      float sum = 0.0f;
+      for (int c = 0; c < top; ++c) {
+        const float e = expf(score_s[warp][ids[(size_t)t * top + c]] - m);
+        weights[(size_t)t * top + c] = e;
+        sum += e;
+      }
+      for (int c = 0; c < top; ++c) weights[(size_t)t * top + c] /= sum;
+    }
+    return;
+  }
   float m = -INFINITY;
   for (int i = lane; i < n; i += 32) m = fmaxf(m, zr[i]);
   m = warp_max(m);
@@ -168,9 +211,10 @@ __device__ __forceinline__ void dot_lanes_rows(const float* const (&w)[NR], cons
 
 constexpr int kMoeWarps = 8;
 
-template <typename T>
+template <typename T, bool GLU>
 __global__ void moe_up_kernel(const T* __restrict__ h, const T* __restrict__ w_up, const int* __restrict__ ids,
-                              T* __restrict__ act, int top, int experts, int width, int ff, int rows_per_block) {
+                              T* __restrict__ act, int top, int experts, int width, int ff, int rows_per_block,
+                              float limit, float slope) {
   extern __shared__ __align__(16) float h_s[];
   const int p = blockIdx.x;
   const int e = ids[p];
@@ -180,7 +224,7 @@ __global__ void moe_up_kernel(const T* __restrict__ h, const T* __restrict__ w_u
   __syncthreads();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int f0 = blockIdx.y * rows_per_block;
-  const T* w = w_up + (size_t)e * ff * width;
+  const T* w = w_up + (size_t)e * (GLU ? 2 : 1) * ff * width;
   const int last = min(ff, f0 + rows_per_block) - 1;
   for (int f = f0 + warp; f <= last; f += 4 * kMoeWarps) {           // four rows of a warp at a time
     const T* rows[4];
@@ -188,6 +232,21 @@ __global__ void moe_up_kernel(const T* __restrict__ h, const T* __restrict__ w_u
 #pragma unroll
     for (int r = 0; r < 4; ++r) rows[r] = w + (size_t)min(f + r * kMoeWarps, last) * width;
     dot_lanes_rows<4>(rows, h_s, width, lane, z);
+    if (GLU) {
+      float up[4];
+#pragma unroll
+      for (int r = 0; r < 4; ++r) rows[r] += (size_t)ff * width;     // the up rows lie ff rows below the gate rows
+      dot_lanes_rows<4>(rows, h_s, width, lane, up);
+      if (lane == 0) {
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+          const float g = fminf(z[r], limit), u = fminf(fmaxf(up[r], -limit), limit);
+          if (f + r * kMoeWarps <= last)
+            act[(size_t)p * ff + f + r * kMoeWarps] = from_f32<T>(g / (1.0f + expf(-slope * g)) * (u + 1.0f));
+        }
+      }
+      continue;
+    }
     if (lane == 0) {
 #pragma unroll
       for (int r = 0; r < 4; ++r) {
@@ -322,20 +381,37 @@ using namespace ifx;
 
 extern "C" {
 
-int ifx_moe_route(const float* z, const float* correction, int* ids, float* weights, int T, int n, int top,
-                  cudaStream_t stream) {
+int ifx_moe_route_ex(const float* z, const float* correction, int* ids, float* weights, int T, int n, int top,
+                     int of_chosen, cudaStream_t stream) {
   if (T <= 0) return 0;
   if (n <= 0 || top <= 0 || top > n) return IFX_E_BADARG;
   if (n > kMaxRouterOutputs) return IFX_E_TOOBIG;
-  moe_route_kernel<<<(T + 3) / 4, 128, 0, stream>>>(z, correction, ids, weights, T, n, top);
+  moe_route_kernel<<<(T + 3) / 4, 128, 0, stream>>>(z, correction, ids, weights, T, n, top, of_chosen);
   IFX_CHECK_LAUNCH();
   return 0;
 }
 
+int ifx_moe_route(const float* z, const float* correction, int* ids, float* weights, int T, int n, int top,
+                  cudaStream_t stream) {
+  return ifx_moe_route_ex(z, correction, ids, weights, T, n, top, 0, stream);
+}
+
 // h [T, width], act [T * top, ff] in `dtype`; out [T, width] in out_dtype.
+int ifx_moe_experts_ex(const void* h, const void* w_up, const void* w_down, const int* ids, const float* weights,
+                       void* act, void* out, int T, int top, int experts, int width, int ff, int dtype, int out_dtype,
+                       int glu, float limit, float slope, cudaStream_t stream);
+
 int ifx_moe_experts(const void* h, const void* w_up, const void* w_down, const int* ids, const float* weights,
                     void* act, void* out, int T, int top, int experts, int width, int ff, int dtype, int out_dtype,
                     cudaStream_t stream) {
+  return ifx_moe_experts_ex(h, w_up, w_down, ids, weights, act, out, T, top, experts, width, ff, dtype, out_dtype, 0, 0.0f,
+                            0.0f, stream);
+}
+
+// glu: w_up is [experts, 2 ff, width], an expert's gate rows above its up rows, and the activation is the clamped gated one.
+int ifx_moe_experts_ex(const void* h, const void* w_up, const void* w_down, const int* ids, const float* weights,
+                       void* act, void* out, int T, int top, int experts, int width, int ff, int dtype, int out_dtype,
+                       int glu, float limit, float slope, cudaStream_t stream) {
   if (T <= 0) return 0;
   if (top <= 0 || experts < 0 || width <= 0 || ff <= 0) return IFX_E_BADARG;
   if ((size_t)width * 4 > 160 * 1024 || (size_t)ff * 4 > 160 * 1024) return IFX_E_TOOBIG;
@@ -345,10 +421,10 @@ int ifx_moe_experts(const void* h, const void* w_up, const void* w_down, const i
 #define IFX_MOE(TT, TO)                                                                                           \
   do {                                                                                                            \
     if (experts > 0) {                                                                                            \
-      auto up = moe_up_kernel<TT>;                                                                                \
+      auto up = glu ? moe_up_kernel<TT, true> : moe_up_kernel<TT, false>;                                         \
       if (smem_up > 48 * 1024) cudaFuncSetAttribute(up, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_up); \
       up<<<grid_up, kMoeWarps * 32, smem_up, stream>>>((const TT*)h, (const TT*)w_up, ids, (TT*)act, top, experts, \
-                                                       width, ff, up_rows);                                       \
+                                                       width, ff, up_rows, limit, slope);                         \
     }                                                                                                             \
     auto down = moe_down_kernel<TT, TO>;                                                                          \
     if (smem_down > 48 * 1024)                                                                                    \

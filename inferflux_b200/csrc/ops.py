@@ -147,8 +147,12 @@ class CudaKernels:
                    "ifx_attention_generic_ex", "ifx_norm_rope_append", "ifx_token_shift_mix", "ifx_cast_rows",
                    "ifx_wkv_scan", "ifx_moe_route", "ifx_moe_experts", "ifx_tanh_rows",
                    "ifx_attention_prefill_bf16_ex", "ifx_attention_decode_bf16_ex", "ifx_moe_sorted_rows", "ifx_moe_sort",
-                   "ifx_moe_gather", "ifx_moe_combine", "ifx_gemm_tcgen05_grouped", "ifx_attention_prefill_tcgen05_ex"):
+                   "ifx_moe_gather", "ifx_moe_combine", "ifx_gemm_tcgen05_grouped", "ifx_attention_prefill_tcgen05_ex",
+                   "ifx_groupnorm_stream", "ifx_residual_add_scaled", "ifx_gelu_mul_table", "ifx_embed_scaled", "ifx_scale_f32",
+                   "ifx_delta_rule_scan", "ifx_latent_rope_append", "ifx_latent_attention_generic_rot", "ifx_moe_route_ex",
+                   "ifx_moe_experts_ex"):
             getattr(self.lib, fn).restype = ctypes.c_int
+        self.lib.ifx_delta_rule_scratch_floats.restype = ctypes.c_longlong
         self.lib.ifx_sample_scratch_bytes.restype = ctypes.c_longlong
         self.lib.ifx_latent_attention_mma_workspace.restype = ctypes.c_longlong
         # latent attention on the tensor-core tiles (0: the per-token kernel, for comparisons)
@@ -186,18 +190,31 @@ class CudaKernels:
         self.native_layer_calls = 0
 
     # ------------------------------------------------------------- elementwise
-    def embed(self, table, token_ids, vocab):
+    def embed(self, table, token_ids, vocab, scale=1.0):
         T, H = token_ids.numel(), table.shape[1]
         out = torch.empty((T, H), dtype=torch.float32, device=table.device)
+        if scale != 1.0:
+            _check(self.lib.ifx_embed_scaled(_ptr(table), _ptr(token_ids), _ptr(out), T, H, int(vocab), ctypes.c_float(scale),
+                                             _DT[table.dtype], _stream()), "embed")
+            self.launches += 1
+            return out
         _check(self.lib.ifx_embed(_ptr(table), _ptr(token_ids), _ptr(out), T, H, int(vocab), _DT[table.dtype],
                                   _stream()), "embed")
         self.launches += 1
         return out
 
-    def rmsnorm(self, x, w, eps, out_dtype):
+    def rmsnorm(self, x, w, eps, out_dtype, groups=1):
         _need(x.dtype == torch.float32 and w.dtype == torch.float32, "rmsnorm: x and w must be float32")
         T, H = x.shape
         out = torch.empty((T, H), dtype=out_dtype, device=x.device)
+        if groups > 1:
+            _need(x.is_contiguous() and H % groups == 0, "rmsnorm: the groups must cut a contiguous row evenly")
+            _check(self.lib.ifx_groupnorm_stream(
+                _ptr(x), _ptr(None), _ptr(None), ctypes.c_float(0.0), _ptr(w), ctypes.c_float(eps), int(groups), _ptr(out),
+                _ptr(None), T, H, 0, _DT[out_dtype], 1, _ptr(None), 0, _ptr(None), ctypes.c_longlong(0), _ptr(None),
+                _ptr(None), _stream()), "rmsnorm (groups)")
+            self.launches += 1
+            return out
         _check(self.lib.ifx_rmsnorm(_ptr(x), _ptr(None), _ptr(w), _ptr(out), T, H, ctypes.c_float(eps), 0,
                                     _DT[out_dtype], _stream()), "rmsnorm")
         self.launches += 1
@@ -821,13 +838,18 @@ class CudaKernels:
         self.launches += 1
 
     # ------------------------------------------- layers that norm a sublayer's output
-    def postnorm_add(self, x, y, w_post, eps_post, w_next=None, eps_next=0.0, out_dtype=None, conv=None, cast_out=False):
+    def postnorm_add(self, x, y, w_post, eps_post, w_next=None, eps_next=0.0, out_dtype=None, conv=None, cast_out=False,
+                     groups=1, both=False):
         """x += y / rms(y) * w_post (x float32, in place).  With `w_next`, also returns the next norm of the
         updated rows, x / rms(x) * w_next in `out_dtype`: sum and both norms in one kernel.  With `cast_out`
         (and no `w_next`) it returns the updated rows themselves in `out_dtype`, for a sublayer that reads
         x without a norm.  `conv` =
         (weight [hidden, taps], taps, state, index, ctx), allowed when every request of the step brings one token
-        (`ctx.max_span == 1`): the rows come back as h + conv(h) over time, and the state has moved on."""
+        (`ctx.max_span == 1`): the rows come back as h + conv(h) over time, and the state has moved on.
+        `groups`: the next norm's root mean square is taken per group of the row.  `both` (with `conv`): returns
+        (h, h + conv(h))."""
+        if groups > 1 or both:
+            return self._postnorm_add_groups(x, y, w_post, eps_post, w_next, eps_next, out_dtype, conv, groups, both)
         splits = 1
         if isinstance(y, PartialSum):                      # the slices are added in the same pass
             _need(tuple(y.shape) == tuple(x.shape), "postnorm_add: partial sums do not match x")
@@ -855,6 +877,92 @@ class CudaKernels:
             _ptr(x), _ptr(y), _ptr(w_post), ctypes.c_float(eps_post), _ptr(w_next), ctypes.c_float(eps_next), _ptr(out),
             T, H, _DT[y.dtype], _DT[(out_dtype or y.dtype)], splits, _ptr(cw), taps, st_ptr, ctypes.c_longlong(stride),
             _ptr(treq), _ptr(rslot), _stream()), "postnorm_add")
+        self.launches += 1
+        return out
+
+    def _postnorm_add_groups(self, x, y, w_post, eps_post, w_next, eps_next, out_dtype, conv, groups, both):
+        splits = 1
+        if isinstance(y, PartialSum):
+            _need(tuple(y.shape) == tuple(x.shape), "postnorm_add: partial sums do not match x")
+            out_dtype = out_dtype or y.dtype
+            y, splits = y.parts, y.splits
+        _need(x.dtype == torch.float32 and x.is_contiguous() and y.is_contiguous() and tuple(y.shape[-2:]) == tuple(x.shape),
+              "postnorm_add: x must be float32 and y of its shape")
+        _need(w_next is not None and w_post.dtype == torch.float32 and w_next.dtype == torch.float32,
+              "postnorm_add: a norm over groups needs both float32 norm weights")
+        T, H = x.shape
+        out_dtype = out_dtype or y.dtype
+        out = torch.empty((T, H), dtype=out_dtype, device=x.device)
+        out2, cw, taps, st_ptr, stride, treq, rslot = None, None, 0, ctypes.c_void_p(0), 0, None, None
+        if conv is not None:
+            cw, taps, state, index, ctx = conv
+            _need(ctx.max_span == 1 and tuple(cw.shape) == (H, taps) and cw.dtype == torch.float32,
+                  "postnorm_add: the convolution is fused only into steps of single tokens")
+            if taps > 1:
+                _need(state is not None and state.dtype == torch.float32 and tuple(state.shape[2:]) == (taps - 1, H)
+                      and state.stride(3) == 1 and state.stride(2) == H and 0 <= index < state.shape[1],
+                      "postnorm_add: the state does not fit the convolution")
+                stride = state.stride(0)
+                st_ptr = ctypes.c_void_p(state.data_ptr() + 4 * index * state.stride(1))
+            treq, rslot = ctx.token_req, ctx.req_slot
+            out2 = torch.empty((T, H), dtype=out_dtype, device=x.device)
+        _check(self.lib.ifx_groupnorm_stream(
+            _ptr(x), _ptr(y), _ptr(w_post), ctypes.c_float(eps_post), _ptr(w_next), ctypes.c_float(eps_next), int(groups),
+            _ptr(out), _ptr(out2), T, H, _DT[y.dtype], _DT[out_dtype], splits, _ptr(cw), taps, st_ptr,
+            ctypes.c_longlong(stride), _ptr(treq), _ptr(rslot), _stream()), "postnorm_add (groups)")
+        self.launches += 1
+        if conv is None:
+            return out
+        return (out, out2) if both else out2
+
+    def residual_add_scaled(self, x, a, b, scale, out_dtype=None):
+        """x += scale * (a + b) (x float32, in place; b may be None; a and b tensors of x's shape or PartialSums).  With
+        `out_dtype` also returns the updated rows in that dtype."""
+        T, H = x.shape
+        _need(x.dtype == torch.float32 and x.is_contiguous(), "residual_add_scaled: x must be contiguous float32")
+
+        def operand(v):
+            if v is None:
+                return None, 0, 1
+            if isinstance(v, PartialSum):
+                _need(tuple(v.shape) == (T, H), "residual_add_scaled: partial sums do not match x")
+                return v.parts, 0, v.splits
+            _need(tuple(v.shape) == (T, H) and v.is_contiguous(), "residual_add_scaled: an operand does not match x")
+            return v, _DT[v.dtype], 1
+        pa, da, sa = operand(a)
+        pb, db, sb = operand(b)
+        out = None if out_dtype is None else torch.empty((T, H), dtype=out_dtype, device=x.device)
+        _check(self.lib.ifx_residual_add_scaled(_ptr(x), _ptr(pa), da, sa, _ptr(pb), db, sb, ctypes.c_float(scale), _ptr(out),
+                                                0 if out is None else _DT[out_dtype], T, H, _stream()), "residual_add_scaled")
+        self.launches += 1
+        return out
+
+    def scale_(self, values, factor):
+        """values *= factor, in place (float32)."""
+        _need(values.dtype == torch.float32 and values.is_contiguous(), "scale_: contiguous float32 values")
+        _check(self.lib.ifx_scale_f32(_ptr(values), ctypes.c_longlong(values.numel()), ctypes.c_float(factor), _stream()), "scale_")
+        self.launches += 1
+
+    def gelu_mul_table(self, z, table, token_ids, first_column):
+        """gelu_tanh(z) * table[token, first_column : first_column + z.shape[1]], in z's dtype."""
+        T, dim = z.shape
+        _need(z.is_contiguous() and table.is_contiguous() and table.dtype == z.dtype and token_ids.numel() == T
+              and first_column + dim <= table.shape[1], "gelu_mul_table: rows and table of one dtype, columns inside the table")
+        out = torch.empty_like(z)
+        _check(self.lib.ifx_gelu_mul_table(_ptr(z), _ptr(table), _ptr(token_ids), table.shape[1], int(first_column),
+                                           table.shape[0], _ptr(out), T, dim, _DT[z.dtype], _stream()), "gelu_mul_table")
+        self.launches += 1
+        return out
+
+    def rmsnorm_columns(self, rows, col0, n, w, eps):
+        """Columns col0 .. col0 + n of `rows`, RMS-normed with weight `w` (float32), as a tensor of their own."""
+        T, ld = rows.shape
+        _need(rows.is_contiguous() and w.dtype == torch.float32 and w.numel() == n and col0 + n <= ld,
+              "rmsnorm_columns: the columns must lie inside contiguous rows")
+        out = torch.empty((T, n), dtype=rows.dtype, device=rows.device)
+        _check(self.lib.ifx_latent_norm_append(
+            _ptr(rows), ld, int(col0), _ptr(w), ctypes.c_float(eps), _ptr(None), _ptr(None), _ptr(None), _ptr(None), 0, 0, 0,
+            _ptr(None), _ptr(out), T, n, _DT[rows.dtype], _stream()), "rmsnorm_columns")
         self.launches += 1
         return out
 
@@ -894,11 +1002,11 @@ class CudaKernels:
         _need(h.is_contiguous() and w.dtype == torch.float32 and tuple(w.shape) == (C, taps), "short_conv: bad operands")
         st_ptr, stride = ctypes.c_void_p(0), 0
         if taps > 1:
-            _need(state is not None and state.dtype == torch.float32 and state.is_contiguous()
-                  and tuple(state.shape[2:]) == (taps - 1, C) and 0 <= index < state.shape[1],
+            _need(state is not None and state.dtype == torch.float32 and tuple(state.shape[2:]) == (taps - 1, C)
+                  and state.stride(3) == 1 and state.stride(2) == C and 0 <= index < state.shape[1],
                   "short_conv: the state does not fit the convolution")
-            stride = state.shape[1] * (taps - 1) * C
-            st_ptr = ctypes.c_void_p(state.data_ptr() + 4 * index * (taps - 1) * C)
+            stride = state.stride(0)                       # a slot's rows may be part of a longer state row
+            st_ptr = ctypes.c_void_p(state.data_ptr() + 4 * index * state.stride(1))
         out = torch.empty_like(h)
         _check(self.lib.ifx_short_conv(_ptr(h), _ptr(w), st_ptr, ctypes.c_longlong(stride), _ptr(ctx.token_req),
                                        _ptr(ctx.req_slot), _ptr(ctx.cu_seqlens), _ptr(out), T, ctx.num_requests, C,
@@ -919,19 +1027,26 @@ class CudaKernels:
             base += n
         return {"latent.items": items}
 
-    def linear_heads(self, a, w, heads, k, n, w_is_nk):
+    def linear_heads(self, a, w, heads, k, n, w_is_nk, a_head_stride=None, out=None, out_head_stride=None):
         """One small product per head, heads side by side in the rows of `a` [T, >= heads * k]:
         out[:, h n:(h + 1) n] = a[:, h k:(h + 1) k] . W_h^T with W_h = w[h n:(h + 1) n] of [n, k] (w_is_nk), or
-        a[:, h k:(h + 1) k] . W_h with W_h = w[h k:(h + 1) k] of [k, n].  bfloat16, through the library."""
+        a[:, h k:(h + 1) k] . W_h with W_h = w[h k:(h + 1) k] of [k, n].  bfloat16, through the library.
+        `a_head_stride`: a head's columns begin that far apart in `a` (default k); `out` with `out_head_stride`:
+        the heads' results go into columns of that tensor, that far apart."""
         T, lda = a.shape
+        sa = k if a_head_stride is None else int(a_head_stride)
         _need(a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and a.is_contiguous() and w.is_contiguous(),
               "linear_heads: contiguous bfloat16 operands")
-        _need(tuple(w.shape) == ((heads * n, k) if w_is_nk else (heads * k, n)) and lda >= heads * k,
+        _need(tuple(w.shape) == ((heads * n, k) if w_is_nk else (heads * k, n)) and sa >= k and lda >= (heads - 1) * sa + k,
               "linear_heads: shapes do not fit")
-        out = torch.empty((T, heads * n), dtype=torch.bfloat16, device=a.device)
+        so = n if out_head_stride is None else int(out_head_stride)
+        if out is None:
+            out = torch.empty((T, heads * so), dtype=torch.bfloat16, device=a.device)
+        _need(out.dtype == torch.bfloat16 and out.is_contiguous() and out.shape[0] == T and so >= n
+              and out.shape[1] >= (heads - 1) * so + n, "linear_heads: the output does not fit")
         ldw = k if w_is_nk else n
         _check(self.lib.ifx_gemm_cublas_bf16_batched(
-            _ptr(a), _LL(lda), _LL(k), _ptr(w), _LL(ldw), _LL(k * n), _ptr(out), _LL(heads * n), _LL(n), T, n, k, heads,
+            _ptr(a), _LL(lda), _LL(sa), _ptr(w), _LL(ldw), _LL(k * n), _ptr(out), _LL(out.shape[1]), _LL(so), T, n, k, heads,
             int(bool(w_is_nk)), _stream()), "linear_heads")
         self.library_calls += 1
         return out
@@ -950,15 +1065,52 @@ class CudaKernels:
             _ptr(None), T, rank, _DT[rows.dtype], _stream()), "latent_norm_append")
         self.launches += 1
 
-    def latent_attention(self, q_rows, w_uk, w_uv, sinks, heads, dim, vdim, rank, window, scale, ctx, cache):
-        """Attention over cached latents (see csrc/latent_attention.cu).  `q_rows`: [T, >= heads * dim], the
-        queries in its first columns.  Returns [T, heads * vdim]."""
+    def latent_rope_append(self, rows, col0, rank, rot, w, eps, q, heads, dim, rotary, ctx, cache):
+        """The cached row of every token: [columns col0 .. + rank of `rows`, RMS-normed with `w`; the `rot` columns
+        behind them, turned by the token's position], written at the token's position.  Returns `q`
+        [T, heads (dim + rot)] with every head's last `rot` elements turned the same way (in place)."""
+        T, ld = rows.shape
+        kv, table = cache.kv, cache.block_table
+        _need(kv is not None and table is not None and kv.dtype == rows.dtype and q.dtype == rows.dtype,
+              "latent_rope_append: no cache of the run's dtype")
+        _need(kv.shape[1] == 1 and kv.shape[2] == 1 and kv.shape[4] == rank + rot,
+              "latent_rope_append: the cache is not one plane of latent and turned part")
+        _need(rows.is_contiguous() and q.is_contiguous() and q.shape[0] == T and q.shape[1] >= heads * (dim + rot),
+              "latent_rope_append: contiguous rows")
+        used, inter, mag, freq = 0, 0, 1.0, None
+        if rot and rotary is not None:
+            used, inter, mag, freq = int(rotary.rotary_dim), int(bool(rotary.interleaved)), float(rotary.magnitude), rotary.inv_freq
+            _need(used <= rot and freq.dtype == torch.float32 and freq.numel() == used // 2,
+                  "latent_rope_append: the table does not fit the turned part")
+        write = bool(cache.writes)
+        _check(self.lib.ifx_latent_rope_append(
+            _ptr(rows), ld, int(col0), _ptr(w), ctypes.c_float(eps), _ptr(q), q.shape[1], _ptr(q), q.shape[1], dim + rot, dim,
+            _ptr(freq), used, inter, ctypes.c_float(mag), _ptr(ctx.positions), _ptr(ctx.token_req), _ptr(ctx.req_slot),
+            _ptr(table), table.shape[1], cache.page_size, kv.shape[0], _ptr(kv if write else None), T, rank, rot, heads, dim,
+            _DT[rows.dtype], _stream()), "latent_rope_append")
+        self.launches += 1
+        return q
+
+    def latent_attention(self, q_rows, w_uk, w_uv, sinks, heads, dim, vdim, rank, window, scale, ctx, cache, rot=0):
+        """Attention over cached latents (see csrc/latent_attention.cu).  `q_rows`: [T, >= heads * (dim + rot)], the
+        queries in its first columns, every head's `rot` turned elements behind its `dim` plain ones; cached rows
+        are [latent of `rank`; turned key part of `rot`].  Returns [T, heads * vdim]."""
         T, ldq = q_rows.shape
         kv, table = cache.kv, cache.block_table
         _need(kv is not None and table is not None and kv.dtype == q_rows.dtype, "latent_attention: no cache of the run's dtype")
         _need(q_rows.is_contiguous() and w_uk.is_contiguous() and w_uv.is_contiguous(), "latent_attention: contiguous operands")
         _need(tuple(w_uk.shape) == (heads * dim, rank) and tuple(w_uv.shape) == (heads * vdim, rank),
               "latent_attention: the up-projections do not fit the sizes")
+        _need(kv.shape[4] == rank + rot and ldq >= heads * (dim + rot), "latent_attention: rows do not hold the turned part")
+        if rot:
+            out = torch.empty((T, heads * vdim), dtype=q_rows.dtype, device=q_rows.device)
+            _check(self.lib.ifx_latent_attention_generic_rot(
+                _ptr(q_rows), ldq, _ptr(w_uk), _ptr(w_uv), _ptr(sinks), _ptr(kv), _ptr(table), _ptr(ctx.positions),
+                _ptr(ctx.token_req), _ptr(ctx.req_slot), _ptr(None), _ptr(out), T, heads, dim, vdim, rank, cache.page_size,
+                table.shape[1], kv.shape[0], 0 if window is None else int(window), ctypes.c_float(scale), int(rot),
+                _DT[q_rows.dtype], _stream()), "latent_attention (turned part)")
+            self.launches += 1
+            return out
         if (self.latent_tiles and q_rows.dtype == torch.bfloat16 and self.lib.ifx_latent_attention_mma_supports(rank)
                 and dim % 8 == 0 and vdim % 8 == 0 and ldq % 8 == 0):
             return self._latent_attention_tiles(q_rows, w_uk, w_uv, sinks, heads, dim, vdim, rank, window, scale, ctx, cache)
@@ -1069,24 +1221,62 @@ class CudaKernels:
         self.launches += 1
         return y
 
+    def delta_rule_scan(self, proj, w_raw, w0, a_bias, norm_w, eps, heads, dim, state, ctx, out_dtype):
+        """The recurrence of csrc/delta_rule.cu over every request's tokens.  `proj`: float32 [T, 5 heads dim], the
+        projections r, k, v, g, a side by side; `w_raw`: float32 [T, heads dim]; `state`: float32 [slots, >= heads dim
+        dim] (rows may be further apart), the matrices [head, key channel, value channel], moved on.  Returns
+        out / rms(out) per head * norm_w * sigmoid(g) in `out_dtype`."""
+        T, HD = proj.shape[0], heads * dim
+        _need(proj.dtype == torch.float32 and proj.is_contiguous() and proj.shape[1] >= 5 * HD and w_raw.dtype == torch.float32
+              and w_raw.is_contiguous() and tuple(w_raw.shape) == (T, HD), "delta_rule_scan: float32 projections")
+        for t in (w0, a_bias, norm_w):
+            _need(t.dtype == torch.float32 and t.is_contiguous() and t.numel() == HD, "delta_rule_scan: float32 constants of heads * dim")
+        _need(state is not None and state.dtype == torch.float32 and state.dim() == 2 and state.stride(1) == 1
+              and state.shape[1] >= HD * dim, "delta_rule_scan: the state does not fit the sizes")
+        scratch = torch.empty(int(self.lib.ifx_delta_rule_scratch_floats(T, heads, dim)), dtype=torch.float32, device=proj.device)
+        y = torch.empty((T, HD), dtype=out_dtype, device=proj.device)
+        _check(self.lib.ifx_delta_rule_scan(
+            _ptr(proj), proj.shape[1], _ptr(w_raw), _ptr(w0), _ptr(a_bias), _ptr(norm_w), ctypes.c_float(eps), _ptr(state),
+            ctypes.c_longlong(state.stride(0)), _ptr(ctx.cu_seqlens), _ptr(ctx.req_slot), _ptr(scratch), _ptr(y),
+            ctx.num_requests, T, heads, dim, _DT[out_dtype], _stream()), "delta_rule_scan")
+        self.launches += 3
+        return y
+
     # ------------------------------------------------------- mixture of experts
-    def moe_route(self, z, correction, top):
+    def moe_route(self, z, correction, top, of_chosen=False):
         """(ids int32 [T, top], weights float32 [T, top]) from router logits z float32 [T, n]: softmax scores; the
-        `top` largest of score + correction are chosen, their weights are the scores."""
+        `top` largest of score + correction are chosen, their weights are the scores.  `of_chosen`: the `top`
+        largest of z + correction are chosen, and the weights are the softmax over the chosen logits alone."""
         T, n = z.shape
         _need(z.dtype == torch.float32 and z.is_contiguous() and (correction is None or (correction.dtype == torch.float32
               and correction.numel() == n)), "moe_route: float32 logits and corrections")
         ids = torch.empty((T, top), dtype=torch.int32, device=z.device)
         weights = torch.empty((T, top), dtype=torch.float32, device=z.device)
-        _check(self.lib.ifx_moe_route(_ptr(z), _ptr(correction), _ptr(ids), _ptr(weights), T, n, int(top), _stream()), "moe_route")
+        _check(self.lib.ifx_moe_route_ex(_ptr(z), _ptr(correction), _ptr(ids), _ptr(weights), T, n, int(top), int(bool(of_chosen)),
+                                         _stream()), "moe_route")
         self.launches += 1
         return ids, weights
 
-    def moe_experts(self, h, w_up, w_down, ids, weights, experts, out_dtype):
+    def moe_experts(self, h, w_up, w_down, ids, weights, experts, out_dtype, glu=None):
         """sum over a token's choices of weight * W_down[e] relu(W_up[e] h)^2, or weight * h for e >= experts.
-        w_up [experts, ff, width], w_down [experts, width, ff] in h's dtype."""
+        w_up [experts, ff, width], w_down [experts, width, ff] in h's dtype.  `glu` = (limit, slope): w_up is
+        [experts, 2 ff, width], an expert's gate rows above its up rows, and the activation is
+        g sigmoid(slope g) (u + 1) with g = min(gate, limit), u = clamp(up, -limit, limit)."""
         T, width = h.shape
         top = ids.shape[1]
+        if glu is not None:
+            _need(experts > 0 and w_up.shape[1] % 2 == 0, "moe_experts: gated experts need gate and up rows")
+            ff = w_up.shape[1] // 2
+            _need(h.is_contiguous() and w_up.dtype == h.dtype and w_down.dtype == h.dtype and w_up.is_contiguous()
+                  and w_down.is_contiguous() and tuple(w_up.shape) == (experts, 2 * ff, width)
+                  and tuple(w_down.shape) == (experts, width, ff), "moe_experts: stacked expert weights in the activations' dtype")
+            act = torch.empty((T * top, ff), dtype=h.dtype, device=h.device)
+            out = torch.empty((T, width), dtype=out_dtype, device=h.device)
+            _check(self.lib.ifx_moe_experts_ex(_ptr(h), _ptr(w_up), _ptr(w_down), _ptr(ids), _ptr(weights), _ptr(act), _ptr(out),
+                                               T, top, int(experts), width, ff, _DT[h.dtype], _DT[out_dtype], 1,
+                                               ctypes.c_float(glu[0]), ctypes.c_float(glu[1]), _stream()), "moe_experts (gated)")
+            self.launches += 2
+            return out
         ff = w_up.shape[1] if experts else 1
         _need(h.is_contiguous() and (not experts or (w_up.dtype == h.dtype and w_down.dtype == h.dtype and w_up.is_contiguous()
               and w_down.is_contiguous() and tuple(w_up.shape) == (experts, ff, width) and tuple(w_down.shape) == (experts, width, ff))),
