@@ -839,6 +839,223 @@ def run_design_zeluzen(args, pk):
     return 0
 
 
+# ---------------------------------------------------------------- Benarax beside Zeluzen
+def benarax_config(shape, layers=0):
+    """Benarax at the sizes of `zeluzen_config`: two delta-rule layers (heads of 64), then a latent attention layer (heads of
+    128 + 64 rotated, a latent of 256, queries through a latent of 1,536), the two pairings taking turns; every layer a
+    mixture of 16 gated experts of which a token uses 4, sized so that a token's active feed-forward parameters equal the
+    Qwen2 shape's; norms over 8 groups, a convolution of 4 taps, a token side input of 256 columns a layer."""
+    from inferflux_b200.config import BenaraxConfig
+    s = DESIGN_SHAPES[shape]
+    q = qwen7b_config(s["qwen"])
+    w, inter = s["width"], q.intermediate_size
+    n = layers or q.num_hidden_layers
+    moe = {"kind": "moe", "expert": {"ff": (inter // 4) // 64 * 64, "limit": 7.0}, "router": {"experts": 16, "top": 4}}
+    rot = {"base": 10000.0, "dims": 64, "scaling": {"factor": 40.0, "original": 4096, "fast": 32.0, "slow": 1.0}}
+    out = []
+    for i in range(n):
+        if i % 3 != 2:
+            out.append({"type": "general_delta", "mixer": {"heads": w // 64, "dim": 64, "rank": 64}, "mlp": moe})
+            continue
+        kind = "latent_attention" if (i // 3) % 2 == 0 else "latent_attention_2"
+        out.append({"type": kind, "mixer": {"heads": s["heads"], "dim": 128, "rot_dim": 64, "vdim": 128, "kv_rank": 256,
+                                            "q_rank": 1536, "scale": 192 ** -0.5, "rot": rot}, "mlp": moe})
+    return BenaraxConfig.from_dict({"architecture": "Benarax", "vocab": s["vocab"], "width": w, "norm": {"eps": 1e-6, "groups": 8},
+                                    "canon": {"taps": 4}, "token_side": {"dim": 256}, "embedding": {"scale": 1.0},
+                                    "logit_scale": 1.0, "residual_mult": 1.0, "layers": out})
+
+
+def benarax_costs(cfg, batch, context, tokens):
+    """(bytes a decode step must read or write, FLOPs of a prefill of `tokens`): matrices (a token's experts, and at most
+    all of them), recurrent state in and out, cached latent rows."""
+    w, step_bytes, flops = cfg.width, 0, 0
+    side = cfg.side_dim or 0
+    for layer in cfg.layers:
+        m, mlp = layer["mixer"], layer["mlp"]
+        if layer["type"] == "general_delta":
+            hd, rank = m["heads"] * m["dim"], m.get("rank") or 16
+            params = 6 * hd * w + rank * (w + hd)
+            step_bytes += 2 * batch * m["heads"] * m["dim"] * m["dim"] * 4
+            flops += 6 * tokens * hd * m["dim"]
+        else:
+            H, dq, row = m["heads"], m["dim"] + m["rot_dim"], m["kv_rank"] + m["rot_dim"]
+            params = w * (m["q_rank"] + row) + m["q_rank"] * H * dq + H * (m["dim"] + m["vdim"]) * m["kv_rank"] + H * m["vdim"] * w
+            step_bytes += batch * context * row * 2
+            flops += 2 * H * (row + m["kv_rank"]) * (tokens * (tokens + 1) // 2)
+        params += 2 * side * w
+        step_bytes += 2 * params
+        flops += 2 * tokens * params
+        if mlp:
+            r = mlp["router"]
+            step_bytes += 2 * 3 * w * mlp["expert"]["ff"] * min(r["experts"], batch * r["top"])
+            flops += 2 * tokens * 3 * w * mlp["expert"]["ff"] * r["top"]
+    return step_bytes + 2 * cfg.vocab * w, flops + 2 * cfg.vocab * w
+
+
+def benarax_kernels(kernels, bcfg, zcfg, pk, batch, context, tokens):
+    """The new design's kernels beside the like kernels of the closest models, each alone at the layer's sizes: the
+    delta-rule scan beside Zeluzen's recurrence, latent attention with a rotated part beside Dafolorn's latent attention,
+    gated experts beside Zeluzen's, the norm over groups behind a normed delta beside the norm over the row."""
+    import torch
+    from inferflux_b200.cache import CacheManager
+    from inferflux_b200.config import ScheduleEntry
+    from inferflux_b200.engine.batch import StepContext, StepEntry
+    from inferflux_b200.parts import KVCacheSpec
+    from inferflux_b200.parts.base import RotaryTable
+    dev, bf = "cuda:0", torch.bfloat16
+    hbm, tf = pk["hbm_gbs"] * 1e9, pk["bf16_tflops"] * 1e12
+    dl = next(l for l in bcfg.layers if l["type"] == "general_delta")["mixer"]
+    at = next(l for l in bcfg.layers if l["type"] != "general_delta")["mixer"]
+    moe = next(l["mlp"] for l in bcfg.layers if l["mlp"])
+    zmoe = next(l["mlp"] for l in zcfg.layers if l["mlp"] and l["mlp"]["kind"] == "moe")
+    w, H, D = bcfg.width, dl["heads"], dl["dim"]
+    page, out = 16, {}
+
+    def row(name, ms, bytes_=0, flops=0):
+        roof = max(bytes_ / hbm, flops / tf)
+        out[name] = {"us": round(ms * 1000, 1), "roofline_us": round(roof * 1e6, 1), "frac": round(roof / (ms * 1e-3), 3),
+                     "bound": "hbm" if bytes_ / hbm >= flops / tf else "tensor"}
+
+    def ctx_for(cache, spans, providers=()):
+        entries, starts, slots = [], [], []
+        for rid, n in spans:
+            if rid not in cache:
+                cache.add_request(rid)
+            start = cache.length(rid)
+            cache.reserve(rid, start + n)
+            entries.append(StepEntry(rid, [0] * n, []))
+            starts.append(start)
+            slots.append(cache.slot(rid))
+        ctx = StepContext.build(kernels, bf, dev, entries, starts, slots, cache.drain_table_updates(), providers=providers)
+        for g, (idx, pg) in zip(cache.groups, ctx.table_updates):
+            kernels.scatter_i32(g.table, idx, pg)
+        for (rid, n), start in zip(spans, starts):
+            cache.commit(rid, start + n)
+        return ctx
+
+    class _Sections:                                       # asks the kernel table for the latent kernels' work lists
+        def step_sections(self, ctx):
+            return ctx.kernels.latent_attention_sections(ctx)
+
+    AH, dk, rot, dv, rank = at["heads"], at["dim"], at["rot_dim"], at["vdim"], at["kv_rank"]
+    for what, spans_a, spans_b in (("decode", [(f"r{i}", context - 1) for i in range(batch)], [(f"r{i}", 1) for i in range(batch)]),
+                                   ("prefill", [], [("p", tokens)])):
+        T = sum(n for _r, n in spans_b)
+        keys = sum((context if what == "decode" else (n * (n + 1)) // 2) for _r, n in spans_b)
+        pages = (batch * context if what == "decode" else tokens) // page + 2 * batch + 2
+        cached = batch * context if what == "decode" else tokens
+        for name, extra in (("latent attention with a rotated part", rot), ("latent attention of the closest model", 0)):
+            cache = CacheManager([(KVCacheSpec(1, rank + extra, None, planes=1), None)], page_size=page, num_pages=pages,
+                                 max_seqs=batch, max_seq_len=max(context, tokens) + 16, dtype=bf, device=dev)
+            cache.groups[0].pool.normal_()
+            if spans_a:
+                ctx_for(cache, spans_a)
+            ctx = ctx_for(cache, spans_b, providers=[_Sections()])
+            view = cache.view(ScheduleEntry(0, 0))
+            uk, uv = (torch.randn(AH * dk, rank, device=dev) * 0.05).to(bf), (torch.randn(AH * dv, rank, device=dev) * 0.05).to(bf)
+            q = (torch.randn(T, AH * (dk + extra), device=dev) * 0.3).to(bf)
+            if extra:
+                down = torch.randn(T, rank + extra, device=dev).to(bf)
+                table = RotaryTable(torch.rand(extra // 2, device=dev), extra, True, 1.0)
+                lw = torch.ones(rank, device=dev)
+                queries = kernels.latent_rope_append(down, 0, rank, extra, lw, 1e-6, q, AH, dk, table, ctx, view, vdim=dv)
+                ms = _event_times(lambda: kernels.latent_rope_append(down, 0, rank, extra, lw, 1e-6, q, AH, dk, table, ctx, view, vdim=dv))
+                row(f"latent row: norm, rotation, append, {what}", ms, bytes_=T * (2 * (rank + extra) * 2 + 2 * AH * extra * 2))
+            else:
+                queries = q
+            ms = _event_times(lambda: kernels.latent_attention(queries, uk, uv, None, AH, dk, dv, rank, None, (dk + rot) ** -0.5, ctx,
+                                                               view, rot=extra))
+            row(f"{name}, {what}", ms, bytes_=cached * (rank + extra) * 2 + 2 * T * AH * (dk + dv) * 2 + AH * (dk + dv) * rank * 2,
+                flops=2 * AH * (2 * rank + extra) * keys + 2 * T * AH * (dk + dv) * rank)
+            del cache
+        # the recurrences: state in and out, float32 inputs, scratch rows and the output
+        ctx = type("C", (), {})()
+        cu = [0]
+        for _r, n in spans_b:
+            cu.append(cu[-1] + n)
+        ctx.cu_seqlens = torch.tensor(cu, dtype=torch.int32, device=dev)
+        ctx.req_slot = torch.arange(len(spans_b), dtype=torch.int32, device=dev)
+        ctx.num_requests, ctx.num_tokens = len(spans_b), T
+        state = torch.zeros(batch, H * D * D + w, device=dev)
+        proj = torch.randn(T, 5 * H * D, device=dev) * 0.1
+        w_raw = torch.randn(T, H * D, device=dev)
+        consts = [torch.zeros(H * D, device=dev), torch.zeros(H * D, device=dev), torch.ones(H * D, device=dev)]
+        ms = _event_times(lambda: kernels.delta_rule_scan(proj, w_raw, *consts, 1e-6, H, D, state, ctx, bf))
+        row(f"delta-rule recurrence over {T} tokens ({what})", ms,
+            bytes_=2 * len(spans_b) * H * D * D * 4 + T * H * D * (6 * 4 + 4 * 8 + 2))
+        ins = [torch.randn(T, H * D, device=dev) * 0.1 for _ in range(5)]
+        x = torch.randn(T, w, device=dev)
+        ms = _event_times(lambda: kernels.wkv_scan(*ins, *consts, 1e-6, H, D, state, H * D * D, x, ctx, bf))
+        row(f"recurrence of the closest model over {T} tokens ({what})", ms,
+            bytes_=2 * len(spans_b) * H * D * D * 4 + T * H * D * (5 * 4 + 8 + 2))
+        y = torch.randn(T, w, device=dev).to(bf)
+        wn = torch.ones(w, device=dev)
+        ms = _event_times(lambda: kernels.postnorm_add(x, y, wn, 1e-6, wn, 1e-6, bf, groups=bcfg.norm_groups))
+        row(f"sum of the normed delta + norm over groups, {T} rows", ms, bytes_=T * w * (8 + 2 + 2))
+        ms = _event_times(lambda: kernels.postnorm_add(x, y, wn, 1e-6, wn, 1e-6, bf))
+        row(f"sum of the normed delta + norm of the closest model, {T} rows", ms, bytes_=T * w * (8 + 2 + 2))
+        a, b = torch.randn(T, w, device=dev).to(bf), torch.randn(T, w, device=dev).to(bf)
+        ms = _event_times(lambda: kernels.residual_add_scaled(x, a, b, 0.5, out_dtype=bf))
+        row(f"scaled sum of both sublayers + rows in bfloat16, {T} rows", ms, bytes_=T * w * (8 + 2 + 2 + 2))
+        # the gated experts against the closest model's (both: all matrices a token uses)
+        h = torch.randn(T, w, device=dev).to(bf)
+        for name, cfg_moe, gated in (("gated experts", moe, True), ("experts of the closest model", zmoe, False)):
+            E, top, ff = cfg_moe["router"]["experts"], cfg_moe["router"]["top"], cfg_moe["expert"]["ff"]
+            n_out = E + (0 if gated else cfg_moe["router"].get("identity", 0))
+            up = (torch.randn(E, (2 if gated else 1) * ff, w, device=dev) * 0.02).to(bf)
+            down = (torch.randn(E, w, ff, device=dev) * 0.02).to(bf)
+            z = torch.randn(T, n_out, device=dev)
+            if gated:
+                ids, wts = kernels.moe_route(z, None, top, of_chosen=True)
+                ms = _event_times(lambda: kernels.moe_route(z, None, top, of_chosen=True))
+                row(f"router over the chosen, {T} rows", ms, bytes_=T * (E + 2) * 4)
+                ms = _event_times(lambda: kernels.moe_experts(h, up, down, ids, wts, E, bf, glu=(7.0, 1.702)))
+            else:
+                ids, wts = kernels.moe_route(z, torch.zeros(n_out, device=dev), top)
+                ms = _event_times(lambda: kernels.moe_experts(h, up, down, ids, wts, E, bf))
+            mats = 3 if gated else 2
+            row(f"{name}, {T} rows", ms, bytes_=min(E, T * top) * mats * ff * w * 2, flops=2 * T * top * mats * ff * w)
+            del up, down
+    kernels.check_errors()
+    return out
+
+
+def run_design_benarax(args, pk):
+    """`--design benarax`: decode and prefill throughput of the design at real layer sizes beside Zeluzen, the closest
+    model, at equal width, layer count, vocabulary and active feed-forward parameters, and its kernels beside the like
+    kernels, one JSON line."""
+    import torch
+    page, batch, context = 16, args.batch, min(args.context, 4096)
+    steps, warmup = max(1, args.steps), max(3, args.warmup)
+    result = {"metric": "decode and prefill tokens/s of another design beside the closest model at equal size",
+              "design": args.design, "dtype": "bf16", "n_gpus": 1, "data": "synthetic: random weights, uniform random token ids",
+              "batch": batch, "context": context, "prefill_tokens": PREFILL_TOKENS, "peaks": pk["source"], "shapes": {}}
+    kernels_table = None
+    for shape in ([args.shape] if args.shape in DESIGN_SHAPES and args.shape != "7b" else sorted(DESIGN_SHAPES)):
+        entry = {}
+        for name in ("benarax", "zeluzen"):
+            cfg = benarax_config(shape, args.layers) if name == "benarax" else zeluzen_config(shape, args.layers)
+            longest = context + 4 * (warmup + 3 * steps) + 16 + batch
+            engine = _engine(cfg, page, batch, longest)
+            r = time_decode(engine, cfg, batch, steps, warmup, repeats=3, context=context, e2e=False)
+            pre_ms = time_prefill(engine, cfg, PREFILL_TOKENS, warmup=2, reps=5)
+            step_bytes, flops = (benarax_costs if name == "benarax" else zeluzen_costs)(cfg, batch, r["ctx"], PREFILL_TOKENS)
+            entry[name] = {"decode_tok_s": round(batch * 1000.0 / r["dev_ms"], 1), "decode_ms_per_step": round(r["dev_ms"], 3),
+                           "decode_hbm_frac": round(step_bytes / (r["dev_ms"] * 1e-3) / 1e9 / pk["hbm_gbs"], 3),
+                           "launches_per_step": round(r["launches"], 1),
+                           "prefill_tok_s": round(PREFILL_TOKENS * 1000.0 / pre_ms, 1), "prefill_ms": round(pre_ms, 2),
+                           "prefill_tensor_frac": round(flops / (pre_ms * 1e-3) / 1e12 / pk["bf16_tflops"], 3)}
+            if name == "benarax" and kernels_table is None:
+                kernels_table = benarax_kernels(engine.kernels, cfg, zeluzen_config(shape, args.layers), pk, batch, context,
+                                                PREFILL_TOKENS)
+                entry["kernels"] = kernels_table
+            del engine
+            torch.cuda.empty_cache()
+        result["shapes"][shape] = entry
+    print(json.dumps(result))
+    return 0
+
+
 def _engine(cfg, page, slots, longest, pages=None, chunk=2048):
     import torch
     from inferflux_b200 import Engine
@@ -872,7 +1089,7 @@ def main() -> int:
     ap.add_argument("--no-extras", action="store_true", help="skip the PyTorch baseline and the 1.5B-shape points")
     ap.add_argument("--prefill-only", action="store_true",
                     help="time only the 2,048-token prefill and print a short line (for profiling prefill)")
-    ap.add_argument("--design", default="", choices=["", "dafolorn", "zeluzen"],
+    ap.add_argument("--design", default="", choices=["", "dafolorn", "zeluzen", "benarax"],
                     help="instead of the headline numbers: this design at real layer sizes beside the Qwen2 shape of equal "
                          "size (decode and prefill tokens/s, and its kernels beside the like kernels); --shape picks one size")
     args = ap.parse_args()
@@ -882,6 +1099,8 @@ def main() -> int:
         return run_reference(args, pk)
     if args.design == "zeluzen":
         return run_design_zeluzen(args, pk)
+    if args.design == "benarax":
+        return run_design_benarax(args, pk)
     if args.design:
         return run_design(args, pk)
     if args.gpus != 1:

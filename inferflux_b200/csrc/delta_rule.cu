@@ -10,9 +10,11 @@
 // Three kernels.  delta_prepare (a warp per token and head) makes decay, a * u and u in float32.  delta_scan walks a
 // request's tokens: a column of S (one value channel, all key channels) never meets another column, so a thread keeps
 // one column in registers, a block a group of columns, and the grid is (requests, heads, column groups); the step's
-// vectors of a stretch of tokens are staged in shared memory.  delta_finish (a warp per token and head) norms and
-// gates.  Everything is float32, and every sum runs over key or value channels in index order, so a token's result
-// does not depend on how its request's tokens were cut into steps or on what else is in the batch.
+// vectors of a stretch of tokens are staged in shared memory (rows padded with zeros to whole float4, read as such),
+// and both sums over key channels run as four interleaved partial sums (channels i % 4) so that their additions do not
+// wait for each other.  delta_finish (a warp per token and head) norms and gates.  Everything is float32, and every
+// sum's order is a function of the head size alone, so a token's result does not depend on how its request's tokens
+// were cut into steps or on what else is in the batch.
 #include "common.cuh"
 
 namespace ifx {
@@ -54,7 +56,8 @@ __global__ void __launch_bounds__(128) delta_scan_kernel(
     const float* __restrict__ proj, int ld, const float* __restrict__ decay, const float* __restrict__ au,
     const float* __restrict__ unit, float* __restrict__ state, long long slot_stride, const int* __restrict__ cu_seqlens,
     const int* __restrict__ req_slot, float* __restrict__ o, int heads, int dim, int cols) {
-  extern __shared__ float stage[];                       // [kDeltaStage][5][dim]: r, k, decay, au, u ; then v [kDeltaStage][cols]
+  extern __shared__ __align__(16) float stage[];         // [kDeltaStage][5][dp]: r, k, decay, au, u ; then v [kDeltaStage][cols]
+  const int dp = (dim + 3) & ~3;                         // a staged row, padded with zeros to whole float4
   const int req = blockIdx.x, h = blockIdx.y, j0 = blockIdx.z * cols;
   const int j = j0 + threadIdx.x;
   const bool live = threadIdx.x < cols && j < dim;
@@ -64,19 +67,20 @@ __global__ void __launch_bounds__(128) delta_scan_kernel(
   float S[D];
 #pragma unroll
   for (int i = 0; i < D; ++i) S[i] = (live && i < dim) ? S_mem[(size_t)i * dim + j] : 0.0f;
-  float* v_s = stage + kDeltaStage * 5 * dim;
+  float* v_s = stage + kDeltaStage * 5 * dp;
   for (int t0 = lo; t0 < hi; t0 += kDeltaStage) {
     const int n = min(kDeltaStage, hi - t0);
     __syncthreads();
-    for (int e = threadIdx.x; e < n * dim; e += blockDim.x) {
-      const int tt = e / dim, i = e % dim;
+    for (int e = threadIdx.x; e < n * dp; e += blockDim.x) {
+      const int tt = e / dp, i = e % dp;
       const size_t row = (size_t)(t0 + tt);
-      float* dst = stage + (size_t)tt * 5 * dim;
-      dst[i] = proj[row * ld + h * dim + i];
-      dst[dim + i] = proj[row * ld + HD + h * dim + i];
-      dst[2 * dim + i] = decay[row * HD + h * dim + i];
-      dst[3 * dim + i] = au[row * HD + h * dim + i];
-      dst[4 * dim + i] = unit[row * HD + h * dim + i];
+      float* dst = stage + (size_t)tt * 5 * dp;
+      const bool in = i < dim;
+      dst[i] = in ? proj[row * ld + h * dim + i] : 0.0f;
+      dst[dp + i] = in ? proj[row * ld + HD + h * dim + i] : 0.0f;
+      dst[2 * dp + i] = in ? decay[row * HD + h * dim + i] : 0.0f;
+      dst[3 * dp + i] = in ? au[row * HD + h * dim + i] : 0.0f;
+      dst[4 * dp + i] = in ? unit[row * HD + h * dim + i] : 0.0f;
     }
     for (int e = threadIdx.x; e < n * cols; e += blockDim.x) {
       const int tt = e / cols, c = e % cols;
@@ -85,22 +89,36 @@ __global__ void __launch_bounds__(128) delta_scan_kernel(
     __syncthreads();
     if (!live) continue;
     for (int tt = 0; tt < n; ++tt) {
-      const float* r_s = stage + (size_t)tt * 5 * dim;
-      const float *k_s = r_s + dim, *w_s = r_s + 2 * dim, *au_s = r_s + 3 * dim, *u_s = r_s + 4 * dim;
+      const float4* r_s = reinterpret_cast<const float4*>(stage + (size_t)tt * 5 * dp);
+      const int q4 = dp >> 2;
+      const float4 *k_s = r_s + q4, *w_s = r_s + 2 * q4, *au_s = r_s + 3 * q4, *u_s = r_s + 4 * q4;
       const float vj = v_s[tt * cols + threadIdx.x];
-      float along = 0.0f;
+      float al[4] = {0.0f, 0.0f, 0.0f, 0.0f};                          // partial sums over channels i % 4
 #pragma unroll
-      for (int i = 0; i < D; ++i)
-        if (i < dim) along = fmaf(u_s[i], S[i], along);
-      float out = 0.0f;
-#pragma unroll
-      for (int i = 0; i < D; ++i)
-        if (i < dim) {
-          const float s = fmaf(k_s[i], vj, fmaf(-au_s[i], along, w_s[i] * S[i]));
-          S[i] = s;
-          out = fmaf(s, r_s[i], out);
+      for (int i = 0; i < D; i += 4)
+        if (i < dp) {
+          const float4 u4 = u_s[i >> 2];
+          al[0] = fmaf(u4.x, S[i], al[0]);
+          al[1] = fmaf(u4.y, S[i + 1], al[1]);
+          al[2] = fmaf(u4.z, S[i + 2], al[2]);
+          al[3] = fmaf(u4.w, S[i + 3], al[3]);
         }
-      o[(size_t)(t0 + tt) * HD + h * dim + j] = out;
+      const float along = (al[0] + al[1]) + (al[2] + al[3]);
+      float ou[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+      for (int i = 0; i < D; i += 4)
+        if (i < dp) {
+          const float4 k4 = k_s[i >> 2], w4 = w_s[i >> 2], a4 = au_s[i >> 2], r4 = r_s[i >> 2];
+          S[i] = fmaf(k4.x, vj, fmaf(-a4.x, along, w4.x * S[i]));
+          S[i + 1] = fmaf(k4.y, vj, fmaf(-a4.y, along, w4.y * S[i + 1]));
+          S[i + 2] = fmaf(k4.z, vj, fmaf(-a4.z, along, w4.z * S[i + 2]));
+          S[i + 3] = fmaf(k4.w, vj, fmaf(-a4.w, along, w4.w * S[i + 3]));
+          ou[0] = fmaf(S[i], r4.x, ou[0]);
+          ou[1] = fmaf(S[i + 1], r4.y, ou[1]);
+          ou[2] = fmaf(S[i + 2], r4.z, ou[2]);
+          ou[3] = fmaf(S[i + 3], r4.w, ou[3]);
+        }
+      o[(size_t)(t0 + tt) * HD + h * dim + j] = (ou[0] + ou[1]) + (ou[2] + ou[3]);
     }
   }
   if (live) {
@@ -158,7 +176,7 @@ int ifx_delta_rule_scan(const float* proj, int ld, const float* w_raw, const flo
   while (cols > 32 && (long long)num_requests * heads * ((dim + cols - 1) / cols) < 296) cols /= 2;
   if (cols > 128) cols = 128;
   dim3 grid(num_requests, heads, (dim + cols - 1) / cols);
-  const size_t smem = (size_t)kDeltaStage * (5 * dim + cols) * sizeof(float);
+  const size_t smem = (size_t)kDeltaStage * (5 * ((dim + 3) & ~3) + cols) * sizeof(float);
 #define IFX_SCAN(DD)                                                                                              \
   do {                                                                                                            \
     auto kern = delta_scan_kernel<DD>;                                                                            \

@@ -34,7 +34,7 @@ namespace ifx {
 constexpr int kBM = 128, kBN = 256, kBK = 64, kGemmStages = 4;
 constexpr uint32_t kABytes = kBM * kBK * 2, kBBytes = kBN * kBK * 2, kStageBytes = kABytes + kBBytes;
 
-enum { GEMM_STORE = 0, GEMM_SWIGLU = 1, GEMM_GROUP_RELU2 = 2, GEMM_GROUP_SCALE = 3 };
+enum { GEMM_STORE = 0, GEMM_SWIGLU = 1, GEMM_GROUP_RELU2 = 2, GEMM_GROUP_SCALE = 3, GEMM_GROUP_GLU = 4 };
 
 __device__ __forceinline__ uint64_t gemm_smem_desc(uint32_t addr) {
   // K-major tile of 128-byte rows, 128-byte swizzle: 8-row groups 1024 bytes apart.
@@ -72,9 +72,10 @@ __global__ void __launch_bounds__(192, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                     __nv_bfloat16* __restrict__ out, int M, int N, int K, int up_row_offset, int m_tiles, int n_tiles,
                     int* __restrict__ error_flag, const int* __restrict__ tile_group, int group_rows,
-                    const float* __restrict__ row_scale) {
-  constexpr int OUT_COLS = MODE == GEMM_SWIGLU ? kBN / 2 : kBN;     // output columns a tile makes
-  constexpr bool GROUPED = MODE == GEMM_GROUP_RELU2 || MODE == GEMM_GROUP_SCALE;
+                    const float* __restrict__ row_scale, float glu_limit, float glu_slope) {
+  constexpr bool PAIRED = MODE == GEMM_SWIGLU || MODE == GEMM_GROUP_GLU;   // a tile is 128 gate rows and their 128 up rows
+  constexpr int OUT_COLS = PAIRED ? kBN / 2 : kBN;                  // output columns a tile makes
+  constexpr bool GROUPED = MODE == GEMM_GROUP_RELU2 || MODE == GEMM_GROUP_SCALE || MODE == GEMM_GROUP_GLU;
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + (size_t)kGemmStages * kStageBytes);
@@ -127,7 +128,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
           const uint32_t dst = smem_addr(smem + (size_t)s * kStageBytes), bar = full0 + 8 * s;
           mbar_expect_tx(bar, kStageBytes);
           tma_load_2d(dst, &map_a, kb * kBK, m0, bar);
-          if (MODE == GEMM_SWIGLU) {
+          if (PAIRED) {
             tma_load_2d(dst + kABytes, &map_w, kb * kBK, n0, bar);                       // 128 gate rows
             tma_load_2d(dst + kABytes + kBBytes / 2, &map_w, kb * kBK, up_row_offset + n0, bar);   // 128 up rows
           } else {
@@ -196,13 +197,18 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       for (int c = 0; c < OUT_COLS; c += 16) {
         uint32_t g[16], u[16];
         gemm_tmem_ld16(taddr + c, g);
-        if (MODE == GEMM_SWIGLU) gemm_tmem_ld16(taddr + kBN / 2 + c, u);
+        if (PAIRED) gemm_tmem_ld16(taddr + kBN / 2 + c, u);
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
         float v[16];
 #pragma unroll
         for (int j = 0; j < 16; ++j) {
           v[j] = __uint_as_float(g[j]);
           if (MODE == GEMM_SWIGLU) v[j] = __fdividef(v[j], 1.0f + __expf(-v[j])) * __uint_as_float(u[j]);
+          if (MODE == GEMM_GROUP_GLU) {                               // g sigmoid(slope g) (u + 1), g cut from above, u on both sides
+            const float gate = fminf(v[j], glu_limit);
+            const float up = fminf(fmaxf(__uint_as_float(u[j]), -glu_limit), glu_limit);
+            v[j] = __fdividef(gate, 1.0f + __expf(-glu_slope * gate)) * (up + 1.0f);
+          }
           if (MODE == GEMM_GROUP_RELU2) v[j] = fmaxf(v[j], 0.0f) * fmaxf(v[j], 0.0f);
           if (MODE == GEMM_GROUP_SCALE) v[j] *= factor;
         }
@@ -256,8 +262,8 @@ static int gemm_sm_count() {
 template <int MODE>
 static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mw, void* out, int M, int N, int K, int up_row_offset,
                        int* error_flag, cudaStream_t stream, const int* tile_group = nullptr, int group_rows = 0,
-                       const float* row_scale = nullptr) {
-  constexpr int OUT_COLS = MODE == GEMM_SWIGLU ? kBN / 2 : kBN;
+                       const float* row_scale = nullptr, float glu_limit = 0.0f, float glu_slope = 0.0f) {
+  constexpr int OUT_COLS = (MODE == GEMM_SWIGLU || MODE == GEMM_GROUP_GLU) ? kBN / 2 : kBN;
   const size_t smem = 1024 + (size_t)kGemmStages * kStageBytes + (2 * kGemmStages + 4) * 8 + 16;
   static bool configured = false;
   if (!configured) {
@@ -270,7 +276,7 @@ static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mw, void* out, 
   const int grid = tiles < gemm_sm_count() ? tiles : gemm_sm_count();
   gemm_tcgen05_kernel<MODE><<<grid, 192, smem, stream>>>(ma, mw, reinterpret_cast<__nv_bfloat16*>(out), M, N, K,
                                                          up_row_offset, m_tiles, n_tiles, error_flag, tile_group,
-                                                         group_rows, row_scale);
+                                                         group_rows, row_scale, glu_limit, glu_slope);
   IFX_CHECK_LAUNCH();
   return 0;
 }
@@ -320,4 +326,20 @@ extern "C" int ifx_gemm_tcgen05_grouped(const void* act, const void* W, void* ou
   if (mode == GEMM_GROUP_SCALE)
     return launch_gemm<GEMM_GROUP_SCALE>(ma, mw, out, M, N, K, 0, error_flag, stream, tile_group, group_rows, row_scale);
   return IFX_E_BADARG;
+}
+
+// The gated form of the same: W [groups * 2 ff, K], a group's ff gate rows above its ff up rows; out [M, ff] bfloat16 =
+// g sigmoid(slope g) (u + 1) with g = min(act . gate^T, limit), u = clamp(act . up^T, -limit, limit).
+extern "C" int ifx_gemm_tcgen05_grouped_glu(const void* act, const void* W, void* out, int M, int ff, int K, int groups,
+                                            const int* tile_group, float limit, float slope, int* error_flag,
+                                            cudaStream_t stream) {
+  if (M <= 0 || ff <= 0) return 0;
+  if (K <= 0 || K % 8 || M % kBM || groups <= 0 || error_flag == nullptr || out == nullptr || tile_group == nullptr)
+    return IFX_E_BADARG;
+  CUtensorMap ma, mw;
+  int rc = weight_tensor_map(&mw, W, (long long)groups * 2 * ff, K, 128);
+  if (rc) return rc;
+  rc = make_tensor_map_bf16(&ma, act, M, K, kBM);
+  if (rc) return rc;
+  return launch_gemm<GEMM_GROUP_GLU>(ma, mw, out, M, ff, K, ff, error_flag, stream, tile_group, 2 * ff, nullptr, limit, slope);
 }

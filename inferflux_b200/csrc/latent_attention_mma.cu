@@ -16,8 +16,13 @@
 // unnormalised sum, maximum and denominator in a workspace, and latent_merge_kernel
 // adds them (and the sink) in split order.
 //
-// Sizes: rank a multiple of 16 up to 256; any number of heads (up to 64 share a
-// block); pages of any size.  Everything else goes to the generic kernel.
+// With `rot` > 0 a cached row is [latent of `rank`; `rot` more numbers] and a query row
+// likewise: the scores run over all rank + rot columns, the weighted sum over the first
+// `rank` only (a key part that is no part of the value, a rotated one for instance).
+//
+// Sizes: rank a multiple of 16 up to 256, rot a multiple of 16 up to 64; any number of
+// heads (up to 64 share a block); pages of any size.  Everything else goes to the
+// generic kernel.
 #include "common.cuh"
 
 namespace ifx {
@@ -55,14 +60,15 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 
 // items[i] = (slot, first flat token, tokens, first position): up to 64 consecutive tokens of one request.
 // Block (x, y, z): item x / subs, its tokens [sub * QT, (sub + 1) * QT) with sub = x % subs; heads y * HC ..; key part z.
-template <int RMAX>
+template <int RMAX, int XMAX>
 __global__ void __launch_bounds__(128, 3) latent_attention_mma_kernel(   // 32 .. 128 threads: a warp per 16 rows; three blocks a SM
     const __nv_bfloat16* __restrict__ ql, const __nv_bfloat16* __restrict__ pool, const int* __restrict__ block_table,
     const int4* __restrict__ items, const float* __restrict__ sinks, __nv_bfloat16* __restrict__ out,
     float* __restrict__ part_o, float2* __restrict__ part_ml, int total_rows, int heads, int rank, int page_size,
-    int max_blocks, int num_pages, int window, float scale_log2, int QT, int HC, int subs, int splits) {
+    int max_blocks, int num_pages, int window, float scale_log2, int QT, int HC, int subs, int splits, int rot) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  const int stride = rank + kPad;                                      // elements per shared row
+  const int kw = rank + rot;                                           // a cached row, a query row
+  const int stride = kw + kPad;                                        // elements per shared row
   const int nthreads = blockDim.x, nwarps = nthreads >> 5, rows_blk = nwarps * 16;
   __nv_bfloat16* q_s = reinterpret_cast<__nv_bfloat16*>(smem_raw);     // [rows of the block][stride]
   __nv_bfloat16* c_s = q_s + rows_blk * stride;                        // [2][32][stride]
@@ -87,12 +93,11 @@ __global__ void __launch_bounds__(128, 3) latent_attention_mma_kernel(   // 32 .
     k_lo = lo_all + blockIdx.z * chunk;
     k_hi = min(hi_all, k_lo + chunk);
   }
-  const int chunks_per_row = rank >> 3;                                // 16-byte pieces of a latent
+  const int chunks_per_row = kw >> 3;                                  // 16-byte pieces of a cached row
 
-  // A tile's 32 latents: lane k of every warp finds where key k lies (one table entry), then the warps take
-  // turns at groups of keys, a lane per 16-byte piece, the address coming from the lane that looked it up.
-  const int keys_per_pass = 32 / chunks_per_row;                       // rank <= 256: a latent is at most 32 pieces
-  const int my_key = lane / chunks_per_row, my_piece = lane % chunks_per_row;
+  // A tile's 32 rows: lane k of every warp finds where key k lies (one table entry), then the warps take
+  // turns at stretches of 32 pieces, a lane per 16-byte piece, the address coming from the lane that looked it up.
+  const int pieces = kKeyTile * chunks_per_row;
   auto load_tile = [&](int buf, int key0) {
     __nv_bfloat16* dst = c_s + (size_t)buf * kKeyTile * stride;
     const int key = key0 + lane;
@@ -100,12 +105,13 @@ __global__ void __launch_bounds__(128, 3) latent_attention_mma_kernel(   // 32 .
     if (key < k_hi) {
       int page = table[key / page_size];
       if (page < 0 || page >= num_pages) page = 0;                     // a broken table must not read outside the pool
-      src = (unsigned long long)(pool + ((size_t)page * page_size + key % page_size) * rank);
+      src = (unsigned long long)(pool + ((size_t)page * page_size + key % page_size) * kw);
     }
-    for (int first = warp * keys_per_pass; first < kKeyTile; first += nwarps * keys_per_pass) {
-      const int kk = first + my_key;
-      const unsigned long long from = __shfl_sync(0xffffffffu, src, kk & 31);
-      if (my_key < keys_per_pass && kk < kKeyTile) {
+    for (int first = warp * 32; first < pieces; first += nthreads) {   // the same trips for every lane of a warp
+      const int i = first + lane;
+      const int kk = min(i / chunks_per_row, kKeyTile - 1), my_piece = i % chunks_per_row;
+      const unsigned long long from = __shfl_sync(0xffffffffu, src, kk);
+      if (i < pieces) {
         __nv_bfloat16* d = dst + kk * stride + my_piece * 8;
         if (from) cp_async16(d, reinterpret_cast<const __nv_bfloat16*>(from) + my_piece * 8);
         else *reinterpret_cast<uint4*>(d) = make_uint4(0u, 0u, 0u, 0u);   // finite values: 0 * garbage must not be NaN
@@ -118,7 +124,7 @@ __global__ void __launch_bounds__(128, 3) latent_attention_mma_kernel(   // 32 .
     const int r = i / chunks_per_row, cc = i % chunks_per_row;
     const int qi = r / HC, hi = r % HC;
     __nv_bfloat16* d = q_s + r * stride + cc * 8;
-    if (qi < ntok && hi < nh) cp_async16(d, ql + ((size_t)(t0 + qi) * heads + h0 + hi) * rank + cc * 8);
+    if (qi < ntok && hi < nh) cp_async16(d, ql + ((size_t)(t0 + qi) * heads + h0 + hi) * kw + cc * 8);
     else *reinterpret_cast<uint4*>(d) = make_uint4(0u, 0u, 0u, 0u);
   }
   const int ntiles = k_hi > k_lo ? (k_hi - k_lo + kKeyTile - 1) / kKeyTile : 0;
@@ -146,7 +152,7 @@ __global__ void __launch_bounds__(128, 3) latent_attention_mma_kernel(   // 32 .
   float o[NT][4];
 #pragma unroll
   for (int i = 0; i < NT; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f;
-  const int ksteps = rank >> 4, ntile_o = rank >> 3;
+  const int ksteps = kw >> 4, ntile_o = rank >> 3;
 
   for (int tile = 0; tile < ntiles; ++tile) {
     const int buf = tile & 1, key0 = k_lo + tile * kKeyTile;
@@ -161,7 +167,7 @@ __global__ void __launch_bounds__(128, 3) latent_attention_mma_kernel(   // 32 .
 #pragma unroll
     for (int j = 0; j < 4; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.0f;
 #pragma unroll
-    for (int ks = 0; ks < RMAX / 16; ++ks) {
+    for (int ks = 0; ks < (RMAX + XMAX) / 16; ++ks) {
       if (ks < ksteps) {
         uint32_t a0, a1, a2, a3;
         const int mi = lane >> 3, rr = lane & 7;
@@ -340,22 +346,26 @@ using namespace ifx;
 
 extern "C" {
 
-// 1 if the tiled kernel takes a latent of this size.
-int ifx_latent_attention_mma_supports(int rank) { return rank > 0 && rank % 16 == 0 && rank <= 256; }
+// 1 if the tiled kernel takes a latent of this size (with `rot` more numbers in every row).
+int ifx_latent_attention_mma_supports_rot(int rank, int rot) {
+  return rank > 0 && rank % 16 == 0 && rank <= 256 && rot >= 0 && rot % 16 == 0 && rot <= 64;
+}
+int ifx_latent_attention_mma_supports(int rank) { return ifx_latent_attention_mma_supports_rot(rank, 0); }
 
 // Bytes of float32 workspace the parts of a split launch need: sums [splits, rows, rank] and (max, sum) pairs.
 long long ifx_latent_attention_mma_workspace(int total_rows, int rank, int splits) {
   return splits > 1 ? (long long)splits * total_rows * (rank + 2) * 4 : 0;
 }
 
-// ql, out: [T, heads, rank] bfloat16.  items: [num_items, 4] (slot, first flat token, tokens <= 64, first position).
-// max_item_tokens: the largest token count among the items.  workspace: as ifx_latent_attention_mma_workspace says.
-int ifx_latent_attention_mma(const void* ql, const void* pool, const int* block_table, const int* items, int num_items,
-                             int max_item_tokens, const float* sinks, void* out, void* workspace, int T, int heads,
-                             int rank, int page_size, int max_blocks, int num_pages, int window, float scale,
-                             int splits, cudaStream_t stream) {
+// ql: [T, heads, rank + rot], out: [T, heads, rank] bfloat16; cached rows of rank + rot.  items: [num_items, 4]
+// (slot, first flat token, tokens <= 64, first position).  max_item_tokens: the largest token count among the items.
+// workspace: as ifx_latent_attention_mma_workspace says.
+int ifx_latent_attention_mma_rot(const void* ql, const void* pool, const int* block_table, const int* items, int num_items,
+                                 int max_item_tokens, const float* sinks, void* out, void* workspace, int T, int heads,
+                                 int rank, int rot, int page_size, int max_blocks, int num_pages, int window, float scale,
+                                 int splits, cudaStream_t stream) {
   if (num_items <= 0 || T <= 0) return 0;
-  if (!ifx_latent_attention_mma_supports(rank) || heads <= 0 || page_size <= 0 || max_blocks <= 0 || splits < 1 ||
+  if (!ifx_latent_attention_mma_supports_rot(rank, rot) || heads <= 0 || page_size <= 0 || max_blocks <= 0 || splits < 1 ||
       max_item_tokens < 1 || max_item_tokens > 64 || splits > kMaxSplits)
     return IFX_E_BADARG;
   if (splits > 1 && workspace == nullptr) return IFX_E_BADARG;
@@ -367,22 +377,28 @@ int ifx_latent_attention_mma(const void* ql, const void* pool, const int* block_
   const int total_rows = T * heads;
   dim3 grid((unsigned)(num_items * subs), (unsigned)((heads + HC - 1) / HC), (unsigned)splits);
   if (grid.y > 65535u || grid.z > 65535u) return IFX_E_TOOBIG;
-  const size_t smem = (size_t)(nwarps * 16 + 2 * kKeyTile) * (rank + kPad) * sizeof(__nv_bfloat16);
+  const size_t smem = (size_t)(nwarps * 16 + 2 * kKeyTile) * (rank + rot + kPad) * sizeof(__nv_bfloat16);
   float* part_o = (float*)workspace;
   float2* part_ml = splits > 1 ? (float2*)(part_o + (size_t)splits * total_rows * rank) : nullptr;
   const float scale_log2 = scale * 1.4426950408889634f;
-#define IFX_LAUNCH(RMAX)                                                                                            \
+#define IFX_LAUNCH(RMAX, XMAX)                                                                                      \
   do {                                                                                                              \
-    auto kern = latent_attention_mma_kernel<RMAX>;                                                                  \
-    if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 72 * 1024);       \
+    auto kern = latent_attention_mma_kernel<RMAX, XMAX>;                                                            \
+    if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 88 * 1024);       \
     kern<<<grid, nwarps * 32, smem, stream>>>((const __nv_bfloat16*)ql, (const __nv_bfloat16*)pool, block_table,            \
                                       (const int4*)items, sinks, (__nv_bfloat16*)out, part_o, part_ml, total_rows,  \
                                       heads, rank, page_size, max_blocks, num_pages, window, scale_log2, QT, HC,    \
-                                      subs, splits);                                                                \
+                                      subs, splits, rot);                                                           \
   } while (0)
-  if (rank <= 64) IFX_LAUNCH(64);
-  else if (rank <= 128) IFX_LAUNCH(128);
-  else IFX_LAUNCH(256);
+  if (rot == 0) {
+    if (rank <= 64) IFX_LAUNCH(64, 0);
+    else if (rank <= 128) IFX_LAUNCH(128, 0);
+    else IFX_LAUNCH(256, 0);
+  } else {
+    if (rank <= 64) IFX_LAUNCH(64, 64);
+    else if (rank <= 128) IFX_LAUNCH(128, 64);
+    else IFX_LAUNCH(256, 64);
+  }
 #undef IFX_LAUNCH
   IFX_CHECK_LAUNCH();
   if (splits > 1) {
@@ -391,6 +407,14 @@ int ifx_latent_attention_mma(const void* ql, const void* pool, const int* block_
     IFX_CHECK_LAUNCH();
   }
   return 0;
+}
+
+int ifx_latent_attention_mma(const void* ql, const void* pool, const int* block_table, const int* items, int num_items,
+                             int max_item_tokens, const float* sinks, void* out, void* workspace, int T, int heads,
+                             int rank, int page_size, int max_blocks, int num_pages, int window, float scale,
+                             int splits, cudaStream_t stream) {
+  return ifx_latent_attention_mma_rot(ql, pool, block_table, items, num_items, max_item_tokens, sinks, out, workspace, T,
+                                      heads, rank, 0, page_size, max_blocks, num_pages, window, scale, splits, stream);
 }
 
 }  // extern "C"

@@ -98,6 +98,15 @@ def _need(cond: bool, msg: str) -> None:
 _I, _F, _P, _LL = ctypes.c_int, ctypes.c_float, ctypes.c_void_p, ctypes.c_longlong
 
 
+class TurnedQueries:
+    """Query rows [T, heads (dim + rot)] whose turned parts already lie in `latent`, the rows of queries in latent
+    space [T, heads (rank + rot)] that the tiled latent attention reads."""
+    __slots__ = ("rows", "latent")
+
+    def __init__(self, rows, latent):
+        self.rows, self.latent = rows, latent
+
+
 class _StepArgs(ctypes.Structure):
     """IfxStepArgs of csrc/layer_forward.cu: one step's batch, the same for every layer."""
     _fields_ = ([(n, _I) for n in ("T", "num_decode", "num_tiles", "max_kv_len")]
@@ -150,7 +159,7 @@ class CudaKernels:
                    "ifx_moe_gather", "ifx_moe_combine", "ifx_gemm_tcgen05_grouped", "ifx_attention_prefill_tcgen05_ex",
                    "ifx_groupnorm_stream", "ifx_residual_add_scaled", "ifx_gelu_mul_table", "ifx_embed_scaled", "ifx_scale_f32",
                    "ifx_delta_rule_scan", "ifx_latent_rope_append", "ifx_latent_attention_generic_rot", "ifx_moe_route_ex",
-                   "ifx_moe_experts_ex"):
+                   "ifx_moe_experts_ex", "ifx_gemm_tcgen05_grouped_glu", "ifx_latent_attention_mma_rot", "ifx_latent_attention_mma_supports_rot"):
             getattr(self.lib, fn).restype = ctypes.c_int
         self.lib.ifx_delta_rule_scratch_floats.restype = ctypes.c_longlong
         self.lib.ifx_sample_scratch_bytes.restype = ctypes.c_longlong
@@ -1065,10 +1074,12 @@ class CudaKernels:
             _ptr(None), T, rank, _DT[rows.dtype], _stream()), "latent_norm_append")
         self.launches += 1
 
-    def latent_rope_append(self, rows, col0, rank, rot, w, eps, q, heads, dim, rotary, ctx, cache):
+    def latent_rope_append(self, rows, col0, rank, rot, w, eps, q, heads, dim, rotary, ctx, cache, vdim=None):
         """The cached row of every token: [columns col0 .. + rank of `rows`, RMS-normed with `w`; the `rot` columns
         behind them, turned by the token's position], written at the token's position.  Returns `q`
-        [T, heads (dim + rot)] with every head's last `rot` elements turned the same way (in place)."""
+        [T, heads (dim + rot)] with every head's last `rot` elements turned the same way (in place), or, where the
+        tiled attention kernel takes the sizes (`vdim` given), a `TurnedQueries`: the turned parts then lie in the
+        rows of queries in latent space, [T, heads (rank + rot)], whose other columns `latent_attention` fills."""
         T, ld = rows.shape
         kv, table = cache.kv, cache.block_table
         _need(kv is not None and table is not None and kv.dtype == rows.dtype and q.dtype == rows.dtype,
@@ -1083,18 +1094,26 @@ class CudaKernels:
             _need(used <= rot and freq.dtype == torch.float32 and freq.numel() == used // 2,
                   "latent_rope_append: the table does not fit the turned part")
         write = bool(cache.writes)
+        dst, ld_dst, head_stride, offset, result = q, q.shape[1], dim + rot, dim, q
+        if (rot and vdim is not None and self.latent_tiles and rows.dtype == torch.bfloat16 and dim % 8 == 0 and vdim % 8 == 0
+                and q.shape[1] % 8 == 0 and self.lib.ifx_latent_attention_mma_supports_rot(rank, rot)):
+            dst = torch.empty((T, heads * (rank + rot)), dtype=torch.bfloat16, device=rows.device)
+            ld_dst, head_stride, offset, result = heads * (rank + rot), rank + rot, rank, TurnedQueries(q, dst)
         _check(self.lib.ifx_latent_rope_append(
-            _ptr(rows), ld, int(col0), _ptr(w), ctypes.c_float(eps), _ptr(q), q.shape[1], _ptr(q), q.shape[1], dim + rot, dim,
+            _ptr(rows), ld, int(col0), _ptr(w), ctypes.c_float(eps), _ptr(q), q.shape[1], _ptr(dst), ld_dst, head_stride, offset,
             _ptr(freq), used, inter, ctypes.c_float(mag), _ptr(ctx.positions), _ptr(ctx.token_req), _ptr(ctx.req_slot),
             _ptr(table), table.shape[1], cache.page_size, kv.shape[0], _ptr(kv if write else None), T, rank, rot, heads, dim,
             _DT[rows.dtype], _stream()), "latent_rope_append")
         self.launches += 1
-        return q
+        return result
 
     def latent_attention(self, q_rows, w_uk, w_uv, sinks, heads, dim, vdim, rank, window, scale, ctx, cache, rot=0):
         """Attention over cached latents (see csrc/latent_attention.cu).  `q_rows`: [T, >= heads * (dim + rot)], the
         queries in its first columns, every head's `rot` turned elements behind its `dim` plain ones; cached rows
         are [latent of `rank`; turned key part of `rot`].  Returns [T, heads * vdim]."""
+        turned = None
+        if isinstance(q_rows, TurnedQueries):
+            q_rows, turned = q_rows.rows, q_rows.latent
         T, ldq = q_rows.shape
         kv, table = cache.kv, cache.block_table
         _need(kv is not None and table is not None and kv.dtype == q_rows.dtype, "latent_attention: no cache of the run's dtype")
@@ -1102,6 +1121,9 @@ class CudaKernels:
         _need(tuple(w_uk.shape) == (heads * dim, rank) and tuple(w_uv.shape) == (heads * vdim, rank),
               "latent_attention: the up-projections do not fit the sizes")
         _need(kv.shape[4] == rank + rot and ldq >= heads * (dim + rot), "latent_attention: rows do not hold the turned part")
+        if turned is not None:
+            return self._latent_attention_tiles(q_rows, w_uk, w_uv, sinks, heads, dim, vdim, rank, window, scale, ctx, cache,
+                                                rot=rot, ql=turned)
         if rot:
             out = torch.empty((T, heads * vdim), dtype=q_rows.dtype, device=q_rows.device)
             _check(self.lib.ifx_latent_attention_generic_rot(
@@ -1123,9 +1145,12 @@ class CudaKernels:
         self.launches += 1
         return out
 
-    def _latent_attention_tiles(self, q_rows, w_uk, w_uv, sinks, heads, dim, vdim, rank, window, scale, ctx, cache):
+    def _latent_attention_tiles(self, q_rows, w_uk, w_uv, sinks, heads, dim, vdim, rank, window, scale, ctx, cache, rot=0,
+                                ql=None):
         """bfloat16: queries into latent space (a product per head), the tensor-core kernel over cached latents
-        with all heads of a token tile in one block, the value projection per head on the weighted latents."""
+        with all heads of a token tile in one block, the value projection per head on the weighted latents.
+        With `rot`, `ql` [T, heads (rank + rot)] holds the turned query parts already, behind the columns that the
+        product per head fills."""
         T = q_rows.shape[0]
         kv, table = cache.kv, cache.block_table
         if "latent.items" not in ctx.extra:                # a step context built without the mixer as a provider
@@ -1133,7 +1158,11 @@ class CudaKernels:
             ctx.extra["latent.items"] = torch.tensor(vals, dtype=torch.int32, device=q_rows.device)
             ctx.extra_len["latent.items"] = len(vals)
         items, num_items = ctx.extra["latent.items"], ctx.extra_len["latent.items"] // 4
-        ql = self.linear_heads(q_rows, w_uk, heads, dim, rank, w_is_nk=False)               # [T, heads * rank]
+        if rot:
+            self.linear_heads(q_rows, w_uk, heads, dim, rank, w_is_nk=False, a_head_stride=dim + rot, out=ql,
+                              out_head_stride=rank + rot)
+        else:
+            ql = self.linear_heads(q_rows, w_uk, heads, dim, rank, w_is_nk=False)           # [T, heads * rank]
         win = 0 if window is None else int(window)
         splits = 1
         max_keys = int(ctx.max_kv_len if not win else min(win, ctx.max_kv_len))
@@ -1152,10 +1181,10 @@ class CudaKernels:
             ws = torch.empty(int(self.lib.ifx_latent_attention_mma_workspace(T * heads, rank, splits)), dtype=torch.uint8,
                              device=q_rows.device)
         olat = torch.empty((T, heads * rank), dtype=torch.bfloat16, device=q_rows.device)
-        _check(self.lib.ifx_latent_attention_mma(
+        _check(self.lib.ifx_latent_attention_mma_rot(
             _ptr(ql), _ptr(kv), _ptr(table), _ptr(items), num_items, int(min(self.LATENT_TILE, ctx.max_span)), _ptr(sinks),
-            _ptr(olat), _ptr(ws), T, heads, rank, cache.page_size, table.shape[1], kv.shape[0], win, ctypes.c_float(scale),
-            splits, _stream()), "latent_attention (tiles)")
+            _ptr(olat), _ptr(ws), T, heads, rank, int(rot), cache.page_size, table.shape[1], kv.shape[0], win,
+            ctypes.c_float(scale), splits, _stream()), "latent_attention (tiles)")
         self.launches += 1 + int(splits > 1)
         return self.linear_heads(olat, w_uv, heads, rank, vdim, w_is_nk=True)               # [T, heads * vdim]
 
@@ -1270,6 +1299,9 @@ class CudaKernels:
             _need(h.is_contiguous() and w_up.dtype == h.dtype and w_down.dtype == h.dtype and w_up.is_contiguous()
                   and w_down.is_contiguous() and tuple(w_up.shape) == (experts, 2 * ff, width)
                   and tuple(w_down.shape) == (experts, width, ff), "moe_experts: stacked expert weights in the activations' dtype")
+            if (h.dtype == torch.bfloat16 and T * top >= self.MOE_TILES_MIN_PAIRS and width % 8 == 0 and ff % 8 == 0
+                    and h.data_ptr() % 16 == 0 and os.environ.get("INFERFLUX_B200_MOE_TILES", "1") != "0"):
+                return self._moe_experts_tiles(h, w_up, w_down, ids, weights, experts, out_dtype, glu=glu)
             act = torch.empty((T * top, ff), dtype=h.dtype, device=h.device)
             out = torch.empty((T, width), dtype=out_dtype, device=h.device)
             _check(self.lib.ifx_moe_experts_ex(_ptr(h), _ptr(w_up), _ptr(w_down), _ptr(ids), _ptr(weights), _ptr(act), _ptr(out),
@@ -1295,11 +1327,12 @@ class CudaKernels:
     # From this many (token, choice) pairs on, the experts run as sorted 128-row tiles on the tensor cores.
     MOE_TILES_MIN_PAIRS = 512
 
-    def _moe_experts_tiles(self, h, w_up, w_down, ids, weights, experts, out_dtype):
+    def _moe_experts_tiles(self, h, w_up, w_down, ids, weights, experts, out_dtype, glu=None):
         """bfloat16, many tokens: pairs sorted by expert into stretches of whole 128-row tiles, two grouped tcgen05
-        products (relu^2 in the first one's epilogue, the pair's weight in the second's), then the sum per token."""
+        products (the activation, relu^2 or the gated one of `glu` over tiles of 128 gate rows and their 128 up rows, in
+        the first one's epilogue, the pair's weight in the second's), then the sum per token."""
         T, width = h.shape
-        top, ff = ids.shape[1], w_up.shape[1]
+        top, ff = ids.shape[1], w_up.shape[1] // (2 if glu is not None else 1)
         pairs = T * top
         cap = int(self.lib.ifx_moe_sorted_rows(pairs, int(experts)))
         dev = h.device
@@ -1312,9 +1345,14 @@ class CudaKernels:
         rows = torch.empty((cap, width), dtype=torch.bfloat16, device=dev)
         _check(self.lib.ifx_moe_gather(_ptr(h), _ptr(row_pair), _ptr(rows), cap, top, width, _stream()), "moe_gather")
         act = torch.empty((cap, ff), dtype=torch.bfloat16, device=dev)
-        _check(self.lib.ifx_gemm_tcgen05_grouped(_ptr(rows), _ptr(w_up), _ptr(act), cap, ff, width, int(experts), ff,
-                                                 _ptr(tile_group), _ptr(None), 2, _ptr(self.error_flag), _stream()),
-               "moe experts (up, tiles)")
+        if glu is not None:
+            _check(self.lib.ifx_gemm_tcgen05_grouped_glu(_ptr(rows), _ptr(w_up), _ptr(act), cap, ff, width, int(experts),
+                                                         _ptr(tile_group), ctypes.c_float(glu[0]), ctypes.c_float(glu[1]),
+                                                         _ptr(self.error_flag), _stream()), "moe experts (gate and up, tiles)")
+        else:
+            _check(self.lib.ifx_gemm_tcgen05_grouped(_ptr(rows), _ptr(w_up), _ptr(act), cap, ff, width, int(experts), ff,
+                                                     _ptr(tile_group), _ptr(None), 2, _ptr(self.error_flag), _stream()),
+                   "moe experts (up, tiles)")
         y = torch.empty((cap, width), dtype=torch.float32, device=dev)
         _check(self.lib.ifx_gemm_tcgen05_grouped(_ptr(act), _ptr(w_down), _ptr(y), cap, width, ff, int(experts), width,
                                                  _ptr(tile_group), _ptr(row_scale), 3, _ptr(self.error_flag), _stream()),

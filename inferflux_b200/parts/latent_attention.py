@@ -151,7 +151,8 @@ class LatentAttention(Mixer):
             q = down
         rotary = self.position.rotary(ctx.device) if self.position is not None else None
         # norms the latent, turns the shared key part and every query head's last `rot` elements, stores [c; k_turned]
-        q = k.latent_rope_append(down, col0, self.rank, self.rot, self.latent_norm, self.eps, q, H, self.dk, rotary, ctx, cache)
+        q = k.latent_rope_append(down, col0, self.rank, self.rot, self.latent_norm, self.eps, q, H, self.dk, rotary, ctx, cache,
+                                 vdim=self.dv)
         a = k.latent_attention(q, self.w_uk, self.w_uv, self.sinks, H, self.dk, self.dv, self.rank, self.window,
                                self.scale, ctx, cache, rot=self.rot)            # [T, H dv]
         return k.linear(a, self.w_o, allow_partial=True)

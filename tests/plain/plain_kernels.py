@@ -346,7 +346,7 @@ class PlainKernels:
             page = cache.block_table[slot, pos // P].long()
             cache.kv[page, 0, 0, pos % P, :] = c.to(cache.kv.dtype)
 
-    def latent_rope_append(self, rows, col0, rank, rot, w, eps, q, heads, dim, rotary, ctx, cache):
+    def latent_rope_append(self, rows, col0, rank, rot, w, eps, q, heads, dim, rotary, ctx, cache, vdim=None):
         """The cached row of every token: [columns col0 .. + rank of `rows`, RMS-normed with `w`; the `rot` columns
         behind them, turned by the token's position].  Returns `q` [T, heads (dim + rot)] with every head's last `rot`
         elements turned the same way (q itself may be changed)."""
