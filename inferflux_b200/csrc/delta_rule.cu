@@ -8,13 +8,13 @@
 //   y_t     = o_t / rms(o_t) per head * norm_w * sigmoid(g_t)
 //
 // Three kernels.  delta_prepare (a warp per token and head) makes decay, a * u and u in float32.  delta_scan walks a
-// request's tokens: a column of S (one value channel, all key channels) never meets another column, so a thread keeps
-// one column in registers, a block a group of columns, and the grid is (requests, heads, column groups); the step's
-// vectors of a stretch of tokens are staged in shared memory (rows padded with zeros to whole float4, read as such),
-// and both sums over key channels run as four interleaved partial sums (channels i % 4) so that their additions do not
-// wait for each other.  delta_finish (a warp per token and head) norms and gates.  Everything is float32, and every
-// sum's order is a function of the head size alone, so a token's result does not depend on how its request's tokens
-// were cut into steps or on what else is in the batch.
+// request's tokens: a column of S (one value channel, all key channels) never meets another column, so the grid is
+// (requests, heads, groups of columns); a column's key channels are cut into slices of 16 that neighbouring lanes keep
+// in registers, and the two sums over key channels are added across a column's lanes by shuffles.  The step's vectors
+// of a stretch of tokens arrive by cp.async in one of two buffers while the other is worked on.  delta_finish (a warp
+// per token and head) norms and gates.  Everything is float32, and every sum's order is a function of the head size
+// alone, so a token's result does not depend on how its request's tokens were cut into steps or on what else is in the
+// batch.
 #include "common.cuh"
 
 namespace ifx {
@@ -48,66 +48,117 @@ __global__ void delta_prepare_kernel(const float* __restrict__ proj, int ld, con
   }
 }
 
-constexpr int kDeltaStage = 16;       // tokens staged at a time
+__device__ __forceinline__ void delta_cp_async_4(void* smem, const void* gmem) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((uint32_t)__cvta_generic_to_shared(smem)), "l"(gmem) : "memory");
+}
+__device__ __forceinline__ void delta_cp_async_16(void* smem, const void* gmem) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(smem)), "l"(gmem) : "memory");
+}
+__device__ __forceinline__ void delta_cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void delta_cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
-// D: key channels a thread keeps (>= dim).  Block: `cols` threads, one value channel each.
-template <int D>
-__global__ void __launch_bounds__(128) delta_scan_kernel(
+constexpr int kDeltaR = 16;           // key channels a thread keeps
+constexpr int kDeltaPad = 4;          // floats between the slices of a staged row: their float4 reads meet no bank twice
+constexpr int kDeltaThreads = 128;
+
+// Thread (c, s) = threadIdx.x / KS, threadIdx.x % KS keeps the key channels s * 16 .. s * 16 + 15 of column j0 + c of S
+// in registers; the KS threads of a column lie in neighbouring lanes and add their parts of both sums by shuffles, in
+// an order that the head size alone decides.  Block: 128 threads, of which the first cols * KS (whole warps) compute;
+// all of them bring the vectors of the next `stage` tokens into the other buffer by cp.async while these are worked on.
+template <int KS>
+__global__ void __launch_bounds__(kDeltaThreads) delta_scan_kernel(
     const float* __restrict__ proj, int ld, const float* __restrict__ decay, const float* __restrict__ au,
     const float* __restrict__ unit, float* __restrict__ state, long long slot_stride, const int* __restrict__ cu_seqlens,
-    const int* __restrict__ req_slot, float* __restrict__ o, int heads, int dim, int cols) {
-  extern __shared__ __align__(16) float stage[];         // [kDeltaStage][5][dp]: r, k, decay, au, u ; then v [kDeltaStage][cols]
-  const int dp = (dim + 3) & ~3;                         // a staged row, padded with zeros to whole float4
+    const int* __restrict__ req_slot, float* __restrict__ o, int heads, int dim, int cols, int stage, int vec) {
+  constexpr int R = kDeltaR;
+  constexpr int DP = KS * (R + kDeltaPad);               // a staged row: slice s at s * (R + pad), zeros beyond dim
+  extern __shared__ __align__(16) float smem[];          // 2 x ([stage][5][DP]: r, k, decay, au, u ; [stage][cols]: v)
+  const int buf_floats = stage * (5 * DP + cols);
   const int req = blockIdx.x, h = blockIdx.y, j0 = blockIdx.z * cols;
-  const int j = j0 + threadIdx.x;
-  const bool live = threadIdx.x < cols && j < dim;
+  const int tid = threadIdx.x, c = tid / KS, sl = tid % KS;
+  const int j = j0 + c;
+  const bool computes = (tid & ~31) < cols * KS;         // this warp has columns
+  const bool live = c < cols && j < dim;
   const int HD = heads * dim;
   const int lo = cu_seqlens[req], hi = cu_seqlens[req + 1];
   float* S_mem = state + (long long)req_slot[req] * slot_stride + (size_t)h * dim * dim;
-  float S[D];
+  float S[R];
 #pragma unroll
-  for (int i = 0; i < D; ++i) S[i] = (live && i < dim) ? S_mem[(size_t)i * dim + j] : 0.0f;
-  float* v_s = stage + kDeltaStage * 5 * dp;
-  for (int t0 = lo; t0 < hi; t0 += kDeltaStage) {
-    const int n = min(kDeltaStage, hi - t0);
-    __syncthreads();
-    for (int e = threadIdx.x; e < n * dp; e += blockDim.x) {
-      const int tt = e / dp, i = e % dp;
-      const size_t row = (size_t)(t0 + tt);
-      float* dst = stage + (size_t)tt * 5 * dp;
-      const bool in = i < dim;
-      dst[i] = in ? proj[row * ld + h * dim + i] : 0.0f;
-      dst[dp + i] = in ? proj[row * ld + HD + h * dim + i] : 0.0f;
-      dst[2 * dp + i] = in ? decay[row * HD + h * dim + i] : 0.0f;
-      dst[3 * dp + i] = in ? au[row * HD + h * dim + i] : 0.0f;
-      dst[4 * dp + i] = in ? unit[row * HD + h * dim + i] : 0.0f;
+  for (int i = 0; i < R; ++i) S[i] = (live && sl * R + i < dim) ? S_mem[(size_t)(sl * R + i) * dim + j] : 0.0f;
+  for (int e = tid; e < 2 * buf_floats; e += kDeltaThreads) smem[e] = 0.0f;
+  __syncthreads();
+
+  auto fetch = [&](int b, int t0) {
+    float* dst = smem + (size_t)b * buf_floats;
+    float* v_s = dst + stage * 5 * DP;
+    const int n = min(stage, hi - t0);
+    if (vec) {                                           // dim, ld and cols in whole float4, rows on 16-byte boundaries
+      const int q4 = dim >> 2;
+      for (int e = tid; e < n * q4; e += kDeltaThreads) {
+        const int tt = e / q4, i = (e % q4) << 2;
+        const size_t row = (size_t)(t0 + tt);
+        float* d = dst + (size_t)tt * 5 * DP + i + kDeltaPad * (i / R);
+        delta_cp_async_16(d, proj + row * ld + h * dim + i);
+        delta_cp_async_16(d + DP, proj + row * ld + HD + h * dim + i);
+        delta_cp_async_16(d + 2 * DP, decay + row * HD + h * dim + i);
+        delta_cp_async_16(d + 3 * DP, au + row * HD + h * dim + i);
+        delta_cp_async_16(d + 4 * DP, unit + row * HD + h * dim + i);
+      }
+      const int c4 = cols >> 2;
+      for (int e = tid; e < n * c4; e += kDeltaThreads) {
+        const int tt = e / c4, i = (e % c4) << 2;
+        if (j0 + i < dim) delta_cp_async_16(v_s + tt * cols + i, proj + (size_t)(t0 + tt) * ld + 2 * HD + h * dim + j0 + i);
+      }
+    } else {
+      for (int e = tid; e < n * dim; e += kDeltaThreads) {
+        const int tt = e / dim, i = e % dim;
+        const size_t row = (size_t)(t0 + tt);
+        float* d = dst + (size_t)tt * 5 * DP + i + kDeltaPad * (i / R);
+        delta_cp_async_4(d, proj + row * ld + h * dim + i);
+        delta_cp_async_4(d + DP, proj + row * ld + HD + h * dim + i);
+        delta_cp_async_4(d + 2 * DP, decay + row * HD + h * dim + i);
+        delta_cp_async_4(d + 3 * DP, au + row * HD + h * dim + i);
+        delta_cp_async_4(d + 4 * DP, unit + row * HD + h * dim + i);
+      }
+      for (int e = tid; e < n * cols; e += kDeltaThreads) {
+        const int tt = e / cols, i = e % cols;
+        if (j0 + i < dim) delta_cp_async_4(v_s + tt * cols + i, proj + (size_t)(t0 + tt) * ld + 2 * HD + h * dim + j0 + i);
+      }
     }
-    for (int e = threadIdx.x; e < n * cols; e += blockDim.x) {
-      const int tt = e / cols, c = e % cols;
-      v_s[tt * cols + c] = j0 + c < dim ? proj[(size_t)(t0 + tt) * ld + 2 * HD + h * dim + j0 + c] : 0.0f;
-    }
+  };
+
+  if (lo < hi) fetch(0, lo);
+  delta_cp_async_commit();
+  int b = 0;
+  for (int t0 = lo; t0 < hi; t0 += stage, b ^= 1) {
+    if (t0 + stage < hi) fetch(b ^ 1, t0 + stage);
+    delta_cp_async_commit();
+    delta_cp_async_wait<1>();                            // everything but the copies just asked for has landed
     __syncthreads();
-    if (!live) continue;
-    for (int tt = 0; tt < n; ++tt) {
-      const float4* r_s = reinterpret_cast<const float4*>(stage + (size_t)tt * 5 * dp);
-      const int q4 = dp >> 2;
-      const float4 *k_s = r_s + q4, *w_s = r_s + 2 * q4, *au_s = r_s + 3 * q4, *u_s = r_s + 4 * q4;
-      const float vj = v_s[tt * cols + threadIdx.x];
-      float al[4] = {0.0f, 0.0f, 0.0f, 0.0f};                          // partial sums over channels i % 4
+    if (computes) {
+      const int n = min(stage, hi - t0);
+      const float* cur = smem + (size_t)b * buf_floats;
+      const float* v_s = cur + stage * 5 * DP;
+      for (int tt = 0; tt < n; ++tt) {
+        const float4* r_s = reinterpret_cast<const float4*>(cur + (size_t)tt * 5 * DP + sl * (R + kDeltaPad));
+        constexpr int Q = DP / 4;
+        const float4 *k_s = r_s + Q, *w_s = r_s + 2 * Q, *au_s = r_s + 3 * Q, *u_s = r_s + 4 * Q;
+        const float vj = c < cols ? v_s[tt * cols + c] : 0.0f;
+        float al[4] = {0.0f, 0.0f, 0.0f, 0.0f};                        // partial sums over channels i % 4
 #pragma unroll
-      for (int i = 0; i < D; i += 4)
-        if (i < dp) {
+        for (int i = 0; i < R; i += 4) {
           const float4 u4 = u_s[i >> 2];
           al[0] = fmaf(u4.x, S[i], al[0]);
           al[1] = fmaf(u4.y, S[i + 1], al[1]);
           al[2] = fmaf(u4.z, S[i + 2], al[2]);
           al[3] = fmaf(u4.w, S[i + 3], al[3]);
         }
-      const float along = (al[0] + al[1]) + (al[2] + al[3]);
-      float ou[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        float along = (al[0] + al[1]) + (al[2] + al[3]);
 #pragma unroll
-      for (int i = 0; i < D; i += 4)
-        if (i < dp) {
+        for (int m = 1; m < KS; m <<= 1) along += __shfl_xor_sync(0xffffffffu, along, m);
+        float ou[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+        for (int i = 0; i < R; i += 4) {
           const float4 k4 = k_s[i >> 2], w4 = w_s[i >> 2], a4 = au_s[i >> 2], r4 = r_s[i >> 2];
           S[i] = fmaf(k4.x, vj, fmaf(-a4.x, along, w4.x * S[i]));
           S[i + 1] = fmaf(k4.y, vj, fmaf(-a4.y, along, w4.y * S[i + 1]));
@@ -118,13 +169,19 @@ __global__ void __launch_bounds__(128) delta_scan_kernel(
           ou[2] = fmaf(S[i + 2], r4.z, ou[2]);
           ou[3] = fmaf(S[i + 3], r4.w, ou[3]);
         }
-      o[(size_t)(t0 + tt) * HD + h * dim + j] = (ou[0] + ou[1]) + (ou[2] + ou[3]);
+        float out = (ou[0] + ou[1]) + (ou[2] + ou[3]);
+#pragma unroll
+        for (int m = 1; m < KS; m <<= 1) out += __shfl_xor_sync(0xffffffffu, out, m);
+        if (live && sl == 0) o[(size_t)(t0 + tt) * HD + h * dim + j] = out;
+      }
     }
+    __syncthreads();                                     // the buffer is filled again two stretches on
   }
+  delta_cp_async_wait<0>();
   if (live) {
 #pragma unroll
-    for (int i = 0; i < D; ++i)
-      if (i < dim) S_mem[(size_t)i * dim + j] = S[i];
+    for (int i = 0; i < R; ++i)
+      if (sl * R + i < dim) S_mem[(size_t)(sl * R + i) * dim + j] = S[i];
   }
 }
 
@@ -171,24 +228,29 @@ int ifx_delta_rule_scan(const float* proj, int ld, const float* w_raw, const flo
   const long long items = (long long)T * heads;
   delta_prepare_kernel<<<(unsigned)((items + 3) / 4), 128, 0, stream>>>(proj, ld, w_raw, w0, a_bias, decay, au, unit, T, heads, dim);
   IFX_CHECK_LAUNCH();
-  // columns a block: all of a head's while (requests x heads) fills the SMs, fewer (at least 32) while it does not
-  int cols = dim < 128 ? ((dim + 31) / 32) * 32 : 128;
-  while (cols > 32 && (long long)num_requests * heads * ((dim + cols - 1) / cols) < 296) cols /= 2;
-  if (cols > 128) cols = 128;
+  // slices of 16 key channels: a function of the head size alone, so that no sum's order depends on anything else
+  const int KS = dim <= 16 ? 1 : dim <= 32 ? 2 : dim <= 64 ? 4 : dim <= 128 ? 8 : 16;
+  // columns a block: as many as its 128 threads take while (requests x heads) fills the SMs, fewer (whole warps) while not
+  const int per_warp = 32 / KS;
+  int cols = kDeltaThreads / KS;
+  while (cols > per_warp && (cols / 2 >= dim || (long long)num_requests * heads * ((dim + cols - 1) / cols) < 296)) cols /= 2;
+  if (per_warp >= 4 && cols < 4) cols = 4;
   dim3 grid(num_requests, heads, (dim + cols - 1) / cols);
-  const size_t smem = (size_t)kDeltaStage * (5 * ((dim + 3) & ~3) + cols) * sizeof(float);
-#define IFX_SCAN(DD)                                                                                              \
+  const int stage = KS <= 8 ? 16 : 8;
+  const int vec = (dim % 4 == 0 && ld % 4 == 0 && cols % 4 == 0 && (uintptr_t)proj % 16 == 0 && (uintptr_t)scratch % 16 == 0) ? 1 : 0;
+  const size_t smem = (size_t)2 * stage * (5 * KS * (kDeltaR + kDeltaPad) + cols) * sizeof(float);
+#define IFX_SCAN(KK)                                                                                              \
   do {                                                                                                            \
-    auto kern = delta_scan_kernel<DD>;                                                                            \
+    auto kern = delta_scan_kernel<KK>;                                                                            \
     if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);     \
-    kern<<<grid, cols, smem, stream>>>(proj, ld, decay, au, unit, state, slot_stride, cu_seqlens, req_slot, o,    \
-                                       heads, dim, cols);                                                         \
+    kern<<<grid, kDeltaThreads, smem, stream>>>(proj, ld, decay, au, unit, state, slot_stride, cu_seqlens, req_slot, o, \
+                                                heads, dim, cols, stage, vec);                                    \
   } while (0)
-  if (dim <= 16) IFX_SCAN(16);
-  else if (dim <= 32) IFX_SCAN(32);
-  else if (dim <= 64) IFX_SCAN(64);
-  else if (dim <= 128) IFX_SCAN(128);
-  else IFX_SCAN(256);
+  if (KS == 1) IFX_SCAN(1);
+  else if (KS == 2) IFX_SCAN(2);
+  else if (KS == 4) IFX_SCAN(4);
+  else if (KS == 8) IFX_SCAN(8);
+  else IFX_SCAN(16);
 #undef IFX_SCAN
   IFX_CHECK_LAUNCH();
   if (out_dtype == IFX_DT_F32)
