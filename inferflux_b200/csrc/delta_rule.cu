@@ -139,7 +139,8 @@ __global__ void __launch_bounds__(kDeltaThreads) delta_scan_kernel(
       const int n = min(stage, hi - t0);
       const float* cur = smem + (size_t)b * buf_floats;
       const float* v_s = cur + stage * 5 * DP;
-      for (int tt = 0; tt < n; ++tt) {
+#pragma unroll 2
+      for (int tt = 0; tt < n; ++tt) {                   // unrolled: a token's output sum runs beside the next token's first sum
         const float4* r_s = reinterpret_cast<const float4*>(cur + (size_t)tt * 5 * DP + sl * (R + kDeltaPad));
         constexpr int Q = DP / 4;
         const float4 *k_s = r_s + Q, *w_s = r_s + 2 * Q, *au_s = r_s + 3 * Q, *u_s = r_s + 4 * Q;

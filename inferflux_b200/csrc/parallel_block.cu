@@ -11,8 +11,8 @@
 //   embed_scaled          out[t] = table[token[t]] * scale in float32
 //   scale_f32             v *= factor
 //
-// One block per row; every reduction is a block reduction of fixed order over a block whose size depends on the
-// width alone, so a row's result does not depend on which other rows share the launch.
+// One block per row; every reduction is a block's (or, per group, a warp's) reduction of fixed order over a block whose
+// size is fixed, so a row's result does not depend on which other rows share the launch.
 #include "common.cuh"
 
 namespace ifx {
@@ -58,14 +58,22 @@ __global__ void __launch_bounds__(256) groupnorm_stream_kernel(
   if (out == nullptr) return;
   __syncthreads();
   const int gs = hidden / groups;
-  for (int g = 0; g < groups; ++g) {                     // a group after the other: each sum has the block's fixed order
+  if (groups == 1) {
     float ss = 0.0f;
-    for (int i = threadIdx.x; i < gs; i += blockDim.x) {
-      const float v = row_s[g * gs + i];
-      ss = fmaf(v, v, ss);
-    }
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) ss = fmaf(row_s[i], row_s[i], ss);
     ss = block_sum(ss, scratch);
-    if (threadIdx.x == 0) scale_s[g] = rsqrtf(ss / (float)gs + eps_next);
+    if (threadIdx.x == 0) scale_s[0] = rsqrtf(ss / (float)hidden + eps_next);
+  } else {                                               // a warp per group: lane order, then the shuffle tree
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+    for (int g = warp; g < groups; g += nwarps) {
+      float ss = 0.0f;
+      for (int i = lane; i < gs; i += 32) {
+        const float v = row_s[g * gs + i];
+        ss = fmaf(v, v, ss);
+      }
+      ss = warp_sum(ss);
+      if (lane == 0) scale_s[g] = rsqrtf(ss / (float)gs + eps_next);
+    }
   }
   __syncthreads();
   TO* o = out + row * hidden;
