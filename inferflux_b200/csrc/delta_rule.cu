@@ -72,9 +72,10 @@ template <int N> __device__ __forceinline__ void delta_cp_async_wait() { asm vol
 constexpr int kDeltaR = 8;            // key channels a thread keeps
 constexpr int kDeltaPad = 4;          // floats between the slices of a staged row: their float4 reads meet no bank twice
 constexpr int kDeltaThreads = 128;
+constexpr int kDeltaNC = 2;           // columns a thread keeps: one's shuffles run under the other's multiply-adds
 
-// Thread (c, s) = threadIdx.x / KS, threadIdx.x % KS keeps the key channels s * 8 .. s * 8 + 7 of column j0 + c of S
-// in registers; the KS threads of a column lie in neighbouring lanes and add their parts of both sums by shuffles, in
+// Thread (c, s) = threadIdx.x / KS, threadIdx.x % KS keeps the key channels s * 8 .. s * 8 + 7 of the columns
+// j0 + 2 c and j0 + 2 c + 1 of S in registers; the KS threads of a column lie in neighbouring lanes and add their parts of both sums by shuffles, in
 // an order that the head size alone decides.  Both sums of a token, u^T S and (r * decay)^T S, are taken of the state
 // before the token, so they run side by side and their shuffles overlap.  Block: 128 threads, of which the first cols * KS (whole warps) compute;
 // all of them bring the vectors of the next `stage` tokens into the other buffer by cp.async while these are worked on.
@@ -89,16 +90,21 @@ __global__ void __launch_bounds__(kDeltaThreads) delta_scan_kernel(
   extern __shared__ __align__(16) float smem[];          // 2 x ([stage][5][DP]: r * decay, k, decay, au, u ; [stage][cols]: v ; [stage][2])
   const int buf_floats = stage * (5 * DP + cols + 2);
   const int req = blockIdx.x, h = blockIdx.y, j0 = blockIdx.z * cols;
+  constexpr int NC = kDeltaNC;
   const int tid = threadIdx.x, c = tid / KS, sl = tid % KS;
-  const int j = j0 + c;
-  const bool computes = (tid & ~31) < cols * KS;         // this warp has columns
-  const bool live = c < cols && j < dim;
+  const int j = j0 + c * NC;                             // this thread's first column
+  const bool computes = (tid & ~31) < cols / NC * KS;    // this warp has columns
+  bool live[NC];
+#pragma unroll
+  for (int cc = 0; cc < NC; ++cc) live[cc] = c * NC + cc < cols && j + cc < dim;
   const int HD = heads * dim;
   const int lo = cu_seqlens[req], hi = cu_seqlens[req + 1];
   float* S_mem = state + (long long)req_slot[req] * slot_stride + (size_t)h * dim * dim;
-  float S[R];
+  float S[NC][R];
 #pragma unroll
-  for (int i = 0; i < R; ++i) S[i] = (live && sl * R + i < dim) ? S_mem[(size_t)(sl * R + i) * dim + j] : 0.0f;
+  for (int cc = 0; cc < NC; ++cc)
+#pragma unroll
+    for (int i = 0; i < R; ++i) S[cc][i] = (live[cc] && sl * R + i < dim) ? S_mem[(size_t)(sl * R + i) * dim + j + cc] : 0.0f;
   for (int e = tid; e < 2 * buf_floats; e += kDeltaThreads) smem[e] = 0.0f;
   __syncthreads();
 
@@ -162,46 +168,62 @@ __global__ void __launch_bounds__(kDeltaThreads) delta_scan_kernel(
         const float4* g_s = reinterpret_cast<const float4*>(cur + (size_t)tt * 5 * DP + sl * (R + kDeltaPad));
         constexpr int Q = DP / 4;
         const float4 *k_s = g_s + Q, *w_s = g_s + 2 * Q, *au_s = g_s + 3 * Q, *u_s = g_s + 4 * Q;
-        const float vj = v_s[tt * cols + c];
-        const float2 cc = c_s[tt];
-        float al[4] = {0.0f, 0.0f, 0.0f, 0.0f}, ql[4] = {0.0f, 0.0f, 0.0f, 0.0f};   // partial sums over channels i % 4
+        const float2 c12v = c_s[tt];
+        float vj[NC], along[NC], kept[NC];
 #pragma unroll
-        for (int i = 0; i < R; i += 4) {
-          const float4 u4 = u_s[i >> 2], g4 = g_s[i >> 2];
-          al[0] = fmaf(u4.x, S[i], al[0]);
-          al[1] = fmaf(u4.y, S[i + 1], al[1]);
-          al[2] = fmaf(u4.z, S[i + 2], al[2]);
-          al[3] = fmaf(u4.w, S[i + 3], al[3]);
-          ql[0] = fmaf(g4.x, S[i], ql[0]);
-          ql[1] = fmaf(g4.y, S[i + 1], ql[1]);
-          ql[2] = fmaf(g4.z, S[i + 2], ql[2]);
-          ql[3] = fmaf(g4.w, S[i + 3], ql[3]);
+        for (int cc = 0; cc < NC; ++cc) {
+          vj[cc] = v_s[tt * cols + c * NC + cc];
+          float al[4] = {0.0f, 0.0f, 0.0f, 0.0f}, ql[4] = {0.0f, 0.0f, 0.0f, 0.0f};   // partial sums over channels i % 4
+#pragma unroll
+          for (int i = 0; i < R; i += 4) {
+            const float4 u4 = u_s[i >> 2], g4 = g_s[i >> 2];
+            al[0] = fmaf(u4.x, S[cc][i], al[0]);
+            al[1] = fmaf(u4.y, S[cc][i + 1], al[1]);
+            al[2] = fmaf(u4.z, S[cc][i + 2], al[2]);
+            al[3] = fmaf(u4.w, S[cc][i + 3], al[3]);
+            ql[0] = fmaf(g4.x, S[cc][i], ql[0]);
+            ql[1] = fmaf(g4.y, S[cc][i + 1], ql[1]);
+            ql[2] = fmaf(g4.z, S[cc][i + 2], ql[2]);
+            ql[3] = fmaf(g4.w, S[cc][i + 3], ql[3]);
+          }
+          along[cc] = (al[0] + al[1]) + (al[2] + al[3]);
+          kept[cc] = (ql[0] + ql[1]) + (ql[2] + ql[3]);
         }
-        float along = (al[0] + al[1]) + (al[2] + al[3]);
-        float kept = (ql[0] + ql[1]) + (ql[2] + ql[3]);
 #pragma unroll
         for (int m = 1; m < KS; m <<= 1) {
-          along += __shfl_xor_sync(0xffffffffu, along, m);
-          kept += __shfl_xor_sync(0xffffffffu, kept, m);
+#pragma unroll
+          for (int cc = 0; cc < NC; ++cc) {
+            along[cc] += __shfl_xor_sync(0xffffffffu, along[cc], m);
+            kept[cc] += __shfl_xor_sync(0xffffffffu, kept[cc], m);
+          }
         }
 #pragma unroll
         for (int i = 0; i < R; i += 4) {
           const float4 k4 = k_s[i >> 2], w4 = w_s[i >> 2], a4 = au_s[i >> 2];
-          S[i] = fmaf(-a4.x, along, fmaf(k4.x, vj, w4.x * S[i]));
-          S[i + 1] = fmaf(-a4.y, along, fmaf(k4.y, vj, w4.y * S[i + 1]));
-          S[i + 2] = fmaf(-a4.z, along, fmaf(k4.z, vj, w4.z * S[i + 2]));
-          S[i + 3] = fmaf(-a4.w, along, fmaf(k4.w, vj, w4.w * S[i + 3]));
+#pragma unroll
+          for (int cc = 0; cc < NC; ++cc) {
+            S[cc][i] = fmaf(-a4.x, along[cc], fmaf(k4.x, vj[cc], w4.x * S[cc][i]));
+            S[cc][i + 1] = fmaf(-a4.y, along[cc], fmaf(k4.y, vj[cc], w4.y * S[cc][i + 1]));
+            S[cc][i + 2] = fmaf(-a4.z, along[cc], fmaf(k4.z, vj[cc], w4.z * S[cc][i + 2]));
+            S[cc][i + 3] = fmaf(-a4.w, along[cc], fmaf(k4.w, vj[cc], w4.w * S[cc][i + 3]));
+          }
         }
-        if (live && sl == 0) o[(size_t)(t0 + tt) * HD + h * dim + j] = fmaf(cc.y, vj, fmaf(-cc.x, along, kept));
+        if (sl == 0) {
+#pragma unroll
+          for (int cc = 0; cc < NC; ++cc)
+            if (live[cc]) o[(size_t)(t0 + tt) * HD + h * dim + j + cc] = fmaf(c12v.y, vj[cc], fmaf(-c12v.x, along[cc], kept[cc]));
+        }
       }
     }
     __syncthreads();                                     // the buffer is filled again two stretches on
   }
   delta_cp_async_wait<0>();
-  if (live) {
+#pragma unroll
+  for (int cc = 0; cc < NC; ++cc) {
+    if (!live[cc]) continue;
 #pragma unroll
     for (int i = 0; i < R; ++i)
-      if (sl * R + i < dim) S_mem[(size_t)(sl * R + i) * dim + j] = S[i];
+      if (sl * R + i < dim) S_mem[(size_t)(sl * R + i) * dim + j + cc] = S[cc][i];
   }
 }
 
@@ -254,8 +276,8 @@ int ifx_delta_rule_scan(const float* proj, int ld, const float* w_raw, const flo
   // slices of 8 key channels: a function of the head size alone, so that no sum's order depends on anything else
   const int KS = dim <= 8 ? 1 : dim <= 16 ? 2 : dim <= 32 ? 4 : dim <= 64 ? 8 : dim <= 128 ? 16 : 32;
   // columns a block: as many as its 128 threads take while (requests x heads) fills the SMs, fewer (whole warps) while not
-  const int least = 32 / KS > 4 ? 32 / KS : 4;           // whole warps, and whole float4 of values
-  int cols = kDeltaThreads / KS;
+  const int least = 32 / KS * kDeltaNC > 4 ? 32 / KS * kDeltaNC : 4;      // whole warps, and whole float4 of values
+  int cols = kDeltaThreads / KS * kDeltaNC;
   while (cols > least && (cols / 2 >= dim || (long long)num_requests * heads * ((dim + cols - 1) / cols) < 296)) cols /= 2;
   dim3 grid(num_requests, heads, (dim + cols - 1) / cols);
   const int stage = KS <= 8 ? 16 : 8;                    // tokens a buffer: 62 KB of shared memory at most, 123 KB for KS = 32
