@@ -275,14 +275,26 @@ int ifx_delta_rule_scan(const float* proj, int ld, const float* w_raw, const flo
   IFX_CHECK_LAUNCH();
   // slices of 8 key channels: a function of the head size alone, so that no sum's order depends on anything else
   const int KS = dim <= 8 ? 1 : dim <= 16 ? 2 : dim <= 32 ? 4 : dim <= 64 ? 8 : dim <= 128 ? 16 : 32;
-  // columns a block: as many as its 128 threads take while (requests x heads) fills the SMs, fewer (whole warps) while not
+  // columns a block: as many as its 128 threads take, then fewer (whole warps) as long as all blocks still run at once
   const int least = 32 / KS * kDeltaNC > 4 ? 32 / KS * kDeltaNC : 4;      // whole warps, and whole float4 of values
-  int cols = kDeltaThreads / KS * kDeltaNC;
-  while (cols > least && (cols / 2 >= dim || (long long)num_requests * heads * ((dim + cols - 1) / cols) < 296)) cols /= 2;
-  dim3 grid(num_requests, heads, (dim + cols - 1) / cols);
   const int stage = KS <= 8 ? 16 : 8;                    // tokens a buffer: 62 KB of shared memory at most, 123 KB for KS = 32
+  static int sms = 0;
+  if (!sms) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 1;
+  }
+  auto bytes_for = [&](int c) { return (size_t)2 * stage * (5 * KS * (kDeltaR + kDeltaPad) + c + 2) * sizeof(float); };
+  auto blocks_for = [&](int c) { return (long long)num_requests * heads * ((dim + c - 1) / c); };
+  auto room_for = [&](int c) {                           // blocks that run at once: shared memory, and 80 registers a thread
+    const long long by_smem = (long long)(227 * 1024 / (bytes_for(c) + 1024));
+    return (long long)sms * (by_smem < 1 ? 1 : by_smem > 6 ? 6 : by_smem);
+  };
+  int cols = kDeltaThreads / KS * kDeltaNC;
+  while (cols > least && (cols / 2 >= dim || blocks_for(cols / 2) <= room_for(cols / 2))) cols /= 2;
+  dim3 grid(num_requests, heads, (dim + cols - 1) / cols);
   const int vec = (dim % 4 == 0 && ld % 4 == 0 && cols % 4 == 0 && (uintptr_t)proj % 16 == 0 && (uintptr_t)scratch % 16 == 0) ? 1 : 0;
-  const size_t smem = (size_t)2 * stage * (5 * KS * (kDeltaR + kDeltaPad) + cols + 2) * sizeof(float);
+  const size_t smem = bytes_for(cols);
 #define IFX_SCAN(KK)                                                                                              \
   do {                                                                                                            \
     auto kern = delta_scan_kernel<KK>;                                                                            \

@@ -338,6 +338,7 @@ def _plant(h, tensors, mixer_raw, pairs, eps):
     (96, 3, 16, 16, 24, 32, 40, "interleaved", 16),        # tiles in bfloat16
     (128, 4, 24, 32, 16, 64, 24, "split_half", 16),        # tiles, values shorter than keys
     (160, 2, 8, 64, 40, 48, 56, "interleaved", 8),         # tiles, a rotated part longer than the latent's plain keys
+    (384, 2, 16, 64, 24, 256, 48, "split_half", 16),       # tiles at their largest latent and rotated part
     (96, 5, 12, 6, 20, 20, 28, "split_half", 4),           # sizes the tiles do not take: the per-token kernel
     (96, 1, 16, 8, 16, 40, 16, "interleaved", 16)])
 def test_latent_attention_with_rotated_part_planted_keys(cuda_kernels, dtype, tol, sizes):
