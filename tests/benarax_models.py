@@ -33,7 +33,8 @@ def configs():
     some frequencies alone, blend some and slow some); one head and several; values longer and shorter than keys;
     latents smaller and larger than a head, no multiple of 16; rotated parts longer than the plain part; recurrent
     heads whose product is below, equal to and above the width; layers without feed-forward; routers choosing one,
-    some and all; multipliers that are 1 and that are not."""
+    some and all; multipliers that are 1 and that are not; and one model (F) in which no size is a multiple of 8, the
+    convolution has one tap, a router has one expert and the whole model is the loop."""
     ramp = {"factor": 4.0, "original": 40, "fast": 4.0, "slow": 1.0}
     a = {"architecture": "Benarax", "vocab": 300, "width": 64, "norm": {"eps": 1e-6, "groups": 2}, "canon": {"taps": 3},
          "embedding": {"scale": 2.0}, "logit_scale": 0.5, "residual_mult": 0.5, "token_side": {"dim": 8},
@@ -64,7 +65,14 @@ def configs():
                      scaling={"factor": 3.0, "original": 4, "fast": 2.0, "slow": 1.0})]}
     e = {"architecture": "Benarax", "vocab": 150, "width": 32, "norm": {"eps": 1e-6, "groups": 4}, "canon": {"taps": 3},
          "loop": {"start": 0, "stop": 1, "times": 1}, "layers": [_delta(1, 32, _moe(8, 2, 2))]}
-    return {"A": (a, 8), "B": (b, 16), "C": (c, 4), "D": (d, 16), "E": (e, 8)}
+    f = {"architecture": "Benarax", "vocab": 203, "width": 100, "norm": {"eps": 1e-6, "groups": 5}, "canon": {"taps": 1},
+         "embedding": {"scale": 1.3}, "logit_scale": 0.7, "residual_mult": 0.9, "token_side": {"dim": 6},
+         "loop": {"start": 0, "stop": 3, "times": 2}, "layers": [
+             _latent("latent_attention", 3, 10, 6, 14, 20, 12, _moe(10, 1, 1), 0.5, base=77.0,
+                     scaling={"factor": 3.0, "original": 32, "fast": 4.0, "slow": 1.0}),
+             _delta(3, 12, _moe(18, 5, 5)),
+             _latent("latent_attention_2", 7, 12, 4, 6, 36, 44, None, 0.8, base=1000.0)]}
+    return {"A": (a, 8), "B": (b, 16), "C": (c, 4), "D": (d, 16), "E": (e, 8), "F": (f, 16)}
 
 
 def medium_config():

@@ -293,7 +293,7 @@ def _plain_runner(d, page, pages=None, max_seqs=4, max_seq_len=512):
                        max_seq_len=max_seq_len)
 
 
-@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E", "F"])
 @pytest.mark.parametrize("cutting", ["whole", "tail", "portions", "mixed"])
 def test_engine_host_logic_on_plain_kernels(name, cutting, benarax_dirs):
     d, page, raw = benarax_dirs[name]

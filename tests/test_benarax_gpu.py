@@ -468,7 +468,7 @@ def _check(name, dtype, got, o):
             _bf16_close(f"{name} {rid}", got[rid], o["bfloat16"][rid], o["yard"][rid])
 
 
-@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E", "F"])
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("cutting", ["whole", "tail", "portions", "mixed"])
 def test_step_function_cuttings(name, dtype, cutting, benarax_dirs, oracle, cuda_kernels):
