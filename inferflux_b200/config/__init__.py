@@ -6,7 +6,8 @@ from .qwen2 import Qwen2Config
 from .dafolorn import DafolornConfig
 from .zeluzen import ZeluzenConfig
 from .benarax import BenaraxConfig
+from .radalix import RadalixConfig
 
 __all__ = ["LayerSpec", "ModelPlan", "PartSpec", "ScheduleEntry", "SubPart", "default_schedule", "prenorm_layer", "ConfigError",
            "config_from_dict", "load_config", "register_architecture", "registered_architectures",
-           "resolve_architecture", "Qwen2Config", "DafolornConfig", "ZeluzenConfig", "BenaraxConfig"]
+           "resolve_architecture", "Qwen2Config", "DafolornConfig", "ZeluzenConfig", "BenaraxConfig", "RadalixConfig"]

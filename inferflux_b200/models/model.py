@@ -11,7 +11,7 @@ from typing import Dict, List
 
 import torch
 
-from ..config.plan import ModelPlan
+from ..config.plan import ModelPlan, ScheduleEntry
 from ..parts import build_part, settle_pending
 from ..weights.loader import TensorSpec
 
@@ -31,7 +31,10 @@ class Layer:
         raise AttributeError(name)
 
     def named_parts(self):
-        return [(self.spec.prefix + sub.infix, self.parts[name]) for name, sub in self.spec.parts.items()]
+        out = [(self.spec.prefix + sub.infix, self.parts[name]) for name, sub in self.spec.parts.items()]
+        if self.block.param_specs():                       # a block may own tensors (vectors that scale its sublayers' outputs)
+            out.append((self.spec.prefix, self.block))
+        return out
 
 
 class Model:
@@ -48,10 +51,14 @@ class Model:
         from ..parts.base import Part
         seen = {}
         for _prefix, part in self.named_parts():
-            for p in [part] + list(getattr(part, "sub_parts", lambda: [])()):
+            inner = getattr(part, "sub_parts", None)          # a part made of parts lists them (a block's dict is not that)
+            for p in [part] + (list(inner()) if callable(inner) else []):
                 if type(p).step_sections is not Part.step_sections:
                     seen.setdefault(type(p), p)
         self.section_providers = list(seen.values())
+        # an embedding that keeps something per request gets a state of its own behind the layers' caches
+        spec = getattr(self.embedding, "state_spec", lambda: None)()
+        self.embedding_cache = plan.num_caches if spec is not None else None
 
     # ------------------------------------------------------------------- tensors
     def named_parts(self):
@@ -94,6 +101,8 @@ class Model:
         for c in range(self.plan.num_caches):
             part = self.layers[self.plan.cache_owner_layer(c)].block.cache_part()
             out.append((None, None) if part is None else (part.cache_spec(), part.state_spec()))
+        if self.embedding_cache is not None:
+            out.append((None, self.embedding.state_spec()))
         return out
 
     # --------------------------------------------------------------------- forward
@@ -101,6 +110,8 @@ class Model:
         """Run the step described by `ctx`; `caches.view(entry)` gives the cache of a
         schedule entry.  Returns float32 logits [len(ctx.logit_rows), vocab]."""
         k = ctx.kernels
+        if self.embedding_cache is not None:
+            ctx.embedding_state = caches.view(ScheduleEntry(layer=0, cache=self.embedding_cache)).state
         x = self.embedding.forward(ctx)                       # float32 [T, hidden]
         if self.plan.keeps_embedding_output:                  # a second gather: x itself is updated in place
             ctx.embedding_output = self.embedding.forward(ctx)

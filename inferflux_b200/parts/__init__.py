@@ -2,7 +2,8 @@
 from .base import (Block, FeedForward, KVCacheSpec, Mixer, Norm, NormedDelta, Part, PositionEncoding, RotaryTable,
                    StateSpec, StreamMerge, TimeConv, TokenInput, WeightBuffers, build_part, register_part, registered_parts,
                    settle_pending)
-from . import attention, block, conv, delta_rule, embedding, latent_attention, mlp, moe, norm, rope, token_input, wkv  # noqa: F401  (registration)
+from . import (attention, block, conv, delta_rule, embedding, latent_attention, linear_scan, mlp, moe, norm, pair, rope,
+               token_input, wkv)  # noqa: F401  (registration)
 
 __all__ = ["Block", "FeedForward", "KVCacheSpec", "Mixer", "Norm", "NormedDelta", "Part", "PositionEncoding",
            "RotaryTable", "StateSpec", "StreamMerge", "TimeConv", "TokenInput", "WeightBuffers", "build_part", "register_part",

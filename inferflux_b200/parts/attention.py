@@ -14,8 +14,11 @@ The three projections are stacked at load so that one product makes q, k and v.
 Options that other designs use, all off by default: values of their own head size (`v_head_dim`), an RMS
 norm of every query and key head before the rotation with one weight per side (`qk_norm`), a mask in
 chunks (`chunk`: position p sees the keys from (p // chunk) * chunk on), one more unit in the softmax's
-denominator (`sink`), a layer that projects queries only and reads the keys and values another layer's
-cache holds (`own_kv` False), and other tensor names (`names`).
+denominator (`sink`; "learned": exp of a learned number per head instead of one), a layer that projects queries only
+and reads the keys and values another layer's cache holds (`own_kv` False), a short causal convolution over time on
+every channel of q, k and v right behind the projection (`conv_taps`; the last taps - 1 projected rows are the
+request's state), a query multiplier 1 + coef ln(floor((p + 1) / every) + 1) at position p (`q_temp`), a gate
+sigmoid(W_g h) on the heads' outputs in front of the output projection (`gate`), and other tensor names (`names`).
 """
 from __future__ import annotations
 
@@ -24,7 +27,13 @@ import math
 import torch
 
 from ..weights.loader import TensorSpec
-from .base import KVCacheSpec, Mixer, WeightBuffers, build_part, register_part
+from .base import KVCacheSpec, Mixer, StateSpec, WeightBuffers, build_part, register_part
+
+
+def materialized_rows(kernels, h):
+    """`h` as a tensor, also when the norm in front left its row scale to the product that follows."""
+    make = getattr(kernels, "materialize_rows", None)
+    return make(h) if make is not None and not isinstance(h, torch.Tensor) else h
 
 
 @register_part("mixer", "attention")
@@ -33,12 +42,14 @@ class Attention(Mixer):
     position (a PartSpec of role `position`, or None), qkv_bias (True, False or
     "if_present"), invent_bias (with "if_present": whether random-weights mode makes
     the biases up; default True), scale (None for 1/sqrt(head_dim)), v_head_dim (None: head_dim),
-    qk_norm (None, or {eps}), chunk (None or int), sink (bool), own_kv (default True),
-    names (tensor names of q, k, v, o, q_bias, k_bias, v_bias, q_norm, k_norm)."""
+    qk_norm (None, or {eps}), chunk (None or int), sink (bool, or "learned": a tensor [heads]), own_kv (default True),
+    conv_taps (None or int), q_temp (None, or {coef, every}), gate (None or "sigmoid"),
+    names (tensor names of q, k, v, o, q_bias, k_bias, v_bias, q_norm, k_norm, sink, gate, q_conv, k_conv, v_conv)."""
 
     _NAMES = {"q": "q_proj.weight", "k": "k_proj.weight", "v": "v_proj.weight", "o": "o_proj.weight",
               "q_bias": "q_proj.bias", "k_bias": "k_proj.bias", "v_bias": "v_proj.bias",
-              "q_norm": "q_norm.weight", "k_norm": "k_norm.weight"}
+              "q_norm": "q_norm.weight", "k_norm": "k_norm.weight", "sink": "sink", "gate": "gate_proj.weight",
+              "q_conv": "q_conv.weight", "k_conv": "k_conv.weight", "v_conv": "v_conv.weight"}
 
     takes_scaled_rows = True          # h goes only into the stacked projection
 
@@ -57,7 +68,8 @@ class Attention(Mixer):
         self.nkv = int(p["num_kv_heads"])
         self.d = int(p["head_dim"])
         self.dv = int(p["v_head_dim"]) if p.get("v_head_dim") is not None else self.d
-        self.general = any(p.get(k) for k in ("qk_norm", "chunk", "sink")) or self.dv != self.d or not p.get("own_kv", True)
+        self.general = (any(p.get(k) for k in ("qk_norm", "chunk", "sink", "conv_taps", "q_temp", "gate"))
+                        or self.dv != self.d or not p.get("own_kv", True))
         if self.general:                   # the general kernels take any even size up to 256
             for size in (self.d, self.dv):
                 if size <= 0 or size % 2 or size > 256:
@@ -77,7 +89,18 @@ class Attention(Mixer):
         if self.chunk is not None and self.chunk <= 0:
             raise ValueError(f"attention: chunk must be positive, got {self.chunk}")
         self.sink = bool(p.get("sink", False))
+        self.learned_sink = p.get("sink") == "learned"
         self.own_kv = bool(p.get("own_kv", True))
+        self.taps = None if not p.get("conv_taps") else int(p["conv_taps"])
+        if self.taps is not None and not (self.own_kv and 1 <= self.taps <= 16):
+            raise ValueError("attention: a convolution behind the projections needs keys of its own and 1 to 16 taps")
+        qt = p.get("q_temp")
+        self.q_temp = None if not qt else (float(qt["coef"]), int(qt["every"]))
+        if self.q_temp is not None and self.q_temp[1] < 1:
+            raise ValueError(f"attention: q_temp.every must be at least 1, got {self.q_temp[1]}")
+        self.gate = p.get("gate") or None
+        if self.gate not in (None, "sigmoid"):
+            raise ValueError(f"attention: unknown gate {self.gate!r} (known: sigmoid)")
         if self.general and self.qkv_bias == "if_present":
             self.qkv_bias = False
         if self.general and self.qkv_bias:
@@ -85,6 +108,7 @@ class Attention(Mixer):
         self.names = dict(self._NAMES)
         self.names.update(p.get("names") or {})
         self.w_qkv = self.b_qkv = self.w_o = self.q_norm_w = self.k_norm_w = None
+        self.sink_values = self.w_gate = self.w_conv = None
 
     # ---------------------------------------------------------------- declarations
     def cache_spec(self):
@@ -98,6 +122,12 @@ class Attention(Mixer):
     @property
     def retain_chunk(self):
         return self.spec.params.get("retain_chunk", self.chunk)
+
+    def state_spec(self):
+        """The last taps - 1 rows of the stacked projection, the convolution's inputs before a step's first token."""
+        if self.taps is None or self.taps < 2:
+            return None
+        return StateSpec(((self.taps - 1) * sum(self._sizes()),), torch.float32)
 
     def _sizes(self):
         """Rows of the stacked projection: (query rows, key rows, value rows)."""
@@ -119,6 +149,13 @@ class Attention(Mixer):
             specs[n["q_norm"]] = TensorSpec((self.d,), init="ones")
             if self.own_kv:
                 specs[n["k_norm"]] = TensorSpec((self.d,), init="ones")
+        if self.learned_sink:
+            specs[n["sink"]] = TensorSpec((self.nq,))
+        if self.gate is not None:
+            specs[n["gate"]] = TensorSpec((self.nq * self.dv, self.hidden))
+        if self.taps is not None:
+            for side, size in (("q", q), ("k", k), ("v", v)):
+                specs[n[side + "_conv"]] = TensorSpec((size, self.taps))
         return specs
 
     def load(self, tensors, dtype, device):
@@ -132,7 +169,25 @@ class Attention(Mixer):
         if self.qk_norm_eps is not None:
             layout["q_norm"] = ((self.d,), torch.float32)
             layout["k_norm"] = ((self.d,), torch.float32)
+        if self.learned_sink:
+            layout["sink"] = ((self.nq,), torch.float32)
+        if self.gate is not None:
+            layout["w_gate"] = ((self.nq * self.dv, self.hidden), dtype)
+        if self.taps is not None:
+            layout["w_conv"] = ((q + k + v, self.taps), torch.float32)
         self.buffers = buf = WeightBuffers(device, layout)
+        if self.learned_sink:
+            buf["sink"].copy_(tensors[n["sink"]])
+            self.sink_values = buf["sink"]
+        if self.gate is not None:
+            buf["w_gate"].copy_(tensors[n["gate"]])
+            self.w_gate = buf["w_gate"]
+        if self.taps is not None:                                          # the three convolutions as one over the stacked rows
+            at = 0
+            for side, size in (("q", q), ("k", k), ("v", v)):
+                buf["w_conv"][at:at + size].copy_(tensors[n[side + "_conv"]])
+                at += size
+            self.w_conv = buf["w_conv"]
         at = 0
         for side, size in sides:                                          # each projection into its rows of the stack
             buf["w_qkv"][at:at + size].copy_(tensors[n[side]])
@@ -169,8 +224,16 @@ class Attention(Mixer):
             return k.linear(a, self.w_o, allow_partial=True)
         if self.own_kv != bool(cache.writes):
             raise ValueError("attention: a layer with keys and values of its own writes its cache, one without reads another's")
+        more = {}
+        if self.taps is not None:                          # every channel of q, k and v over time, the state moved on
+            state = None if self.taps < 2 else cache.state.unflatten(1, (1, self.taps - 1, sum(self._sizes())))
+            qkv = k.short_conv(k.materialize(qkv), self.w_conv, self.taps, state, 0, ctx, add_input=False)
+        if self.q_temp is not None:
+            more["q_temp"] = self.q_temp
         q = k.rope_append(qkv, None, rotary, self.nq, self.nkv, self.d, ctx, cache, q_norm=self.q_norm_w,
-                          k_norm=self.k_norm_w, norm_eps=self.qk_norm_eps or 0.0, dv=self.dv, own_kv=self.own_kv)
+                          k_norm=self.k_norm_w, norm_eps=self.qk_norm_eps or 0.0, dv=self.dv, own_kv=self.own_kv, **more)
         a = k.attention(q, self.nq, self.nkv, self.d, self.window, self.scale, ctx, cache, chunk=self.chunk,
-                        sink=self.sink, dv=self.dv)                                             # [T, nq dv]
+                        sink=self.sink_values if self.learned_sink else self.sink, dv=self.dv)   # [T, nq dv]
+        if self.gate is not None:
+            a = k.gate_mul(a, k.linear(materialized_rows(k, h), self.w_gate), self.gate)
         return k.linear(a, self.w_o, allow_partial=True)

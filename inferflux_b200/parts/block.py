@@ -236,6 +236,65 @@ class ParallelBlock(Block):
         return x, self.side.forward(x, ctx, rows=rows)
 
 
+@register_part("block", "parallel_norms")
+class ParallelNormsBlock(Block):
+    """Two norms of the same stream, one in front of each sublayer, and both outputs added at once, each multiplied
+    element by element by a learned vector of the block's own:
+
+        x += s_m * mixer(norm_m(x)) + s_f * ffn(norm_f(x))
+
+    params: ffn (False: the layer has a mixer only), hidden_size, layer_scale (None: no vectors; or tensor names
+    {mixer, ffn}).  Parts: norm_mixer, mixer and, with a feed-forward, norm_ffn, ffn.  A feed-forward may hand back two
+    outputs (a pair: a mixture's and a shared expert's); the sum takes both."""
+
+    def __init__(self, spec, parts):
+        self.has_ffn = bool(spec.params.get("ffn", True))
+        names = {"norm_mixer": "norm", "mixer": "mixer"}
+        if self.has_ffn:
+            names.update({"norm_ffn": "norm", "ffn": "ffn"})
+        self.sub_parts = names
+        super().__init__(spec, parts)
+        self.hidden = int(spec.params["hidden_size"])
+        self.scale_names = spec.params.get("layer_scale") or None
+        self.s_mixer = self.s_ffn = None
+
+    def param_specs(self):
+        if not self.scale_names:
+            return {}
+        specs = {self.scale_names["mixer"]: TensorSpec((self.hidden,), init="ones")}
+        if self.has_ffn:
+            specs[self.scale_names["ffn"]] = TensorSpec((self.hidden,), init="ones")
+        return specs
+
+    def load(self, tensors, dtype, device):
+        if not self.scale_names:
+            return
+        self.s_mixer = tensors[self.scale_names["mixer"]].to(device=device, dtype=torch.float32).contiguous()
+        if self.has_ffn:
+            self.s_ffn = tensors[self.scale_names["ffn"]].to(device=device, dtype=torch.float32).contiguous()
+
+    def forward(self, x, pending, ctx, cache):
+        k = ctx.kernels
+        if self.has_ffn:
+            h_m, h_f = k.rmsnorm_pair(x, self.norm_mixer.weight, self.norm_mixer.eps, self.norm_ffn.weight, self.norm_ffn.eps,
+                                      ctx.dtype, delta=_settled(x, pending, ctx))
+        else:
+            h_m, h_f = self.norm_mixer.forward(x, _settled(x, pending, ctx), ctx), None
+        y = self.mixer.forward(h_m, ctx, cache)
+        f = self.ffn.forward(h_f, ctx) if self.has_ffn else None
+        f, f2 = f if isinstance(f, tuple) else (f, None)
+        k.residual_add_vectors(x, y, self.s_mixer, f, self.s_ffn, f2)
+        return x, None
+
+
+def _settled(x, pending, ctx):
+    """What is left to add inside the next norm kernel: a plain delta is; one with a norm of its own is added here."""
+    if isinstance(pending, NormedDelta):
+        pending.add_to(x, ctx)
+        return None
+    return pending
+
+
 @register_part("merge", "linear_reinject")
 class LinearReinject(StreamMerge):
     """x' = W [x; x0] + step[repeat]: the stream and the embedding output side by side through one matrix

@@ -90,10 +90,11 @@ class PlainKernels:
 
     # --------------------------------------------------------------- attention
     def rope_append(self, qkv, bias, rotary, nq, nkv, d, ctx, cache, q_norm=None, k_norm=None, norm_eps=0.0, dv=None,
-                    own_kv=True):
-        if q_norm is not None or k_norm is not None or (dv is not None and dv != d) or not own_kv:
+                    own_kv=True, q_temp=None):
+        if (q_norm is not None or k_norm is not None or (dv is not None and dv != d) or not own_kv or q_temp is not None
+                or (rotary is not None and rotary.magnitude != 1.0)):
             return self._norm_rope_append(qkv, rotary, nq, nkv, d, d if dv is None else dv, ctx, cache, q_norm, k_norm,
-                                          norm_eps, own_kv)
+                                          norm_eps, own_kv, q_temp)
         T = qkv.shape[0]
         x = qkv.to(self.acc)
         if bias is not None:
@@ -130,6 +131,7 @@ class PlainKernels:
         rot = rotary.rotary_dim
         ang = pos.to(torch.float32)[:, None] * rotary.inv_freq[None, :].to(torch.float32)
         cos, sin = torch.cos(ang).to(self.acc)[:, None, :], torch.sin(ang).to(self.acc)[:, None, :]
+        cos, sin = cos * rotary.magnitude, sin * rotary.magnitude
         part = x[..., :rot]
         if rotary.interleaved:
             a, b = part[..., 0::2], part[..., 1::2]
@@ -139,7 +141,8 @@ class PlainKernels:
             turned = torch.cat([a * cos - b * sin, a * sin + b * cos], dim=-1)
         return torch.cat([turned, x[..., rot:]], dim=-1)
 
-    def _norm_rope_append(self, qkv, rotary, nq, nkv, d, dv, ctx, cache, q_norm, k_norm, norm_eps, own_kv):
+    def _norm_rope_append(self, qkv, rotary, nq, nkv, d, dv, ctx, cache, q_norm, k_norm, norm_eps, own_kv, q_temp=None):
+        """`q_temp` = (coef, every): the queries are multiplied by 1 + coef ln(floor((p + 1) / every) + 1) at position p."""
         T = qkv.shape[0]
         x = qkv.to(self.acc)
         pos = ctx.positions.long()
@@ -149,6 +152,9 @@ class PlainKernels:
                 return v
             return v * torch.rsqrt((v * v).mean(-1, keepdim=True) + norm_eps) * w.to(self.acc)
         q = self._turn(head_norm(x[:, :nq * d].view(T, nq, d), q_norm), rotary, pos)
+        if q_temp is not None:
+            mult = 1.0 + q_temp[0] * torch.log((torch.div(pos + 1, q_temp[1], rounding_mode="floor") + 1).to(torch.float32))
+            q = q * mult.to(self.acc)[:, None, None]
         if own_kv:
             k = self._turn(head_norm(x[:, nq * d:(nq + nkv) * d].view(T, nkv, d), k_norm), rotary, pos)
             v = x[:, (nq + nkv) * d:].view(T, nkv, dv)
@@ -165,7 +171,7 @@ class PlainKernels:
         dv = d if dv is None else dv
         T = q.shape[0]
         P = cache.page_size
-        if chunk or sink or dv != d:
+        if chunk or torch.is_tensor(sink) or sink or dv != d:
             out = torch.empty((T, nq, dv), dtype=q.dtype, device=q.device)
             qv = q.view(T, nq, d).to(self.acc)
             pos_all, req_all, slots = ctx.positions.tolist(), ctx.token_req.tolist(), ctx.req_slot.tolist()
@@ -181,7 +187,9 @@ class PlainKernels:
                 for h in range(nq):
                     g = h // (nq // nkv)
                     s = (K[:, g, :] @ qv[t, h]) * scale
-                    if sink:
+                    if torch.is_tensor(sink):                    # a learned number per head in the denominator
+                        s = torch.cat([s, sink[h].to(s.dtype).reshape(1)])
+                    elif sink:
                         s = torch.cat([s, torch.zeros(1, dtype=s.dtype)])
                     p = torch.softmax(s, dim=0)[:keys.numel()]
                     out[t, h] = (p @ V[:, g, :]).to(q.dtype)
@@ -228,9 +236,13 @@ class PlainKernels:
     def softcap(self, logits, cap):
         logits.copy_(cap * torch.tanh(logits.to(self.acc) / cap))
 
-    def short_conv(self, h, w, taps, state, index, ctx):
+    def short_conv(self, h, w, taps, state, index, ctx, add_input=True, bias=None, act=None, columns=None):
+        """`add_input` False: the convolution alone; `bias` [channels] is added and `act` ("silu") applied behind it;
+        `columns` = (first, count): the convolution runs over those columns of `h` and returns them alone."""
+        if columns is not None:
+            h = h[:, columns[0]:columns[0] + columns[1]]
         ha, wa = h.to(self.acc), w.to(self.acc)
-        out = ha * (1.0 + wa[:, taps - 1])
+        out = ha * ((1.0 if add_input else 0.0) + wa[:, taps - 1])
         cu, slots = ctx.cu_seqlens.tolist(), ctx.req_slot.tolist()
         for r in range(ctx.num_requests):
             lo, hi = cu[r], cu[r + 1]
@@ -241,7 +253,11 @@ class PlainKernels:
             for k in range(1, taps):
                 out[lo:hi] += wa[:, taps - 1 - k] * seq[taps - 1 - k:taps - 1 - k + (hi - lo)]
             state[slots[r], index] = seq[-(taps - 1):].to(state.dtype)
-        return out.to(h.dtype)
+        if bias is not None:
+            out = out + bias.to(self.acc)
+        if act == "silu":
+            out = out * torch.sigmoid(out)
+        return out.to(h.dtype).contiguous()
 
     # ------------------------------------------------- recurrence with matrix state
     def cast_rows(self, x, dtype):
@@ -305,8 +321,111 @@ class PlainKernels:
         out = out * torch.rsqrt((out * out).mean(-1, keepdim=True) + eps)
         return (out.reshape(T, HD) * norm_w.to(A) * torch.sigmoid(g)).to(out_dtype)
 
+    # ------------------------------------------- pairs of mixers, scans with a decayed matrix state
+    def bigram_add(self, x, table, token_ids, state, mul_prev, mul_cur, buckets, vocab, ctx):
+        """x[t] += table[(token before * mul_prev + token * mul_cur) mod buckets], the last row (`buckets`) at position 0;
+        the token before a span's first one is state[slot, 0] (int32), which then takes the span's last token."""
+        ids, pos = token_ids.long(), ctx.positions.long()
+        cu, slots = ctx.cu_seqlens.tolist(), ctx.req_slot.tolist()
+        before = torch.empty_like(ids)
+        for r in range(ctx.num_requests):
+            lo, hi = cu[r], cu[r + 1]
+            before[lo] = state[slots[r], 0]
+            before[lo + 1:hi] = ids[lo:hi - 1]
+            state[slots[r], 0] = ids[hi - 1].to(state.dtype)
+        rows = torch.where(pos == 0, torch.full_like(ids, buckets), (before * mul_prev + ids * mul_cur) % buckets)
+        x += table[rows].to(torch.float32)
+
+    def rmsnorm_pair(self, x, w_a, eps_a, w_b, eps_b, out_dtype, delta=None):
+        """x += delta (if any); two RMS norms of the same rows."""
+        if delta is not None:
+            x += delta.to(torch.float32)
+        return self.rmsnorm(x, w_a, eps_a, out_dtype), self.rmsnorm(x, w_b, eps_b, out_dtype)
+
+    def gate_mul(self, a, g, kind):
+        """a * sigmoid(g) (`sigmoid`) or a * silu(g) (`silu`), in a's dtype."""
+        ga = g.to(self.acc)
+        gate = torch.sigmoid(ga) if kind == "sigmoid" else ga * torch.sigmoid(ga)
+        return (a.to(self.acc) * gate).to(a.dtype)
+
+    def decay_scan(self, q, k, v, raw, state, ctx, heads, groups, dk, dv, decay, tau=1.0, q_scale=1.0, step_bias=None,
+                   log_rate=None, skip=None):
+        """Per request and head a float32 matrix S, kept in `state` [slots, heads dv dk] as [head, value channel, key
+        channel]: S <- diag(w_t) S + k_t v_t^T, o_t = S^T (q_scale q_t) with the new S.  q, k: float32 [T, groups dk]
+        (head h reads group h // (heads / groups)); v: [T, heads dv]; returns float32 [T, heads dv].
+        decay `sigmoid_root`: raw [T, heads dk], w = sigmoid(raw)^(1/tau).
+        decay `softplus_step`: raw [T, heads], dt = softplus(raw + step_bias), w = exp(-exp(log_rate) dt) for the whole
+        head, k is multiplied by dt, and skip[h] v_t is added to o_t."""
+        T, A = q.shape[0], self.acc
+        per = heads // groups
+        of_head = torch.arange(heads) // per
+        qa = q.to(A).reshape(T, groups, dk)[:, of_head] * q_scale
+        ka = k.to(A).reshape(T, groups, dk)[:, of_head]
+        va = v.to(A).reshape(T, heads, dv)
+        if decay == "sigmoid_root":
+            w = torch.exp(torch.nn.functional.logsigmoid(raw.to(A)) / tau).reshape(T, heads, dk)
+        elif decay == "softplus_step":
+            dt = torch.nn.functional.softplus(raw.to(A) + step_bias.to(A), threshold=30.0)
+            w = torch.exp(-torch.exp(log_rate.to(A)) * dt)[:, :, None].expand(T, heads, dk)
+            ka = ka * dt[:, :, None]
+        else:
+            raise ValueError(decay)
+        out = torch.empty((T, heads, dv), dtype=A)
+        cu, slots = ctx.cu_seqlens.tolist(), ctx.req_slot.tolist()
+        for r in range(ctx.num_requests):
+            S = state[slots[r], :heads * dv * dk].to(A).view(heads, dv, dk).clone()
+            for t in range(cu[r], cu[r + 1]):
+                S = w[t][:, None, :] * S + va[t][:, :, None] * ka[t][:, None, :]
+                out[t] = torch.einsum("hvd,hd->hv", S, qa[t])
+            state[slots[r], :heads * dv * dk] = S.reshape(-1).to(state.dtype)
+        if skip is not None:
+            out = out + skip.to(A)[None, :, None] * va
+        return out.reshape(T, heads * dv).to(torch.float32)
+
+    def gated_groupnorm(self, y, gate, w, eps, groups, gate_first, out_dtype):
+        """Rows of y [T, C] in `groups` equal parts, each over its own root mean square, times w (of size C, or of a
+        part's size and then the same for every part) and silu(gate): the gate multiplies before the norm
+        (`gate_first`) or behind it."""
+        A = self.acc
+        ya, ga = y.to(A), gate.to(A)
+        ga = ga * torch.sigmoid(ga)
+        if gate_first:
+            ya = ya * ga
+        T, C = ya.shape
+        parts = ya.reshape(T, groups, C // groups)
+        normed = parts * torch.rsqrt((parts * parts).mean(-1, keepdim=True) + eps)
+        wa = w.to(A)
+        normed = (normed * wa).reshape(T, C) if wa.numel() == C // groups else normed.reshape(T, C) * wa
+        if not gate_first:
+            normed = normed * ga
+        return normed.to(out_dtype)
+
+    def pair_combine(self, a, b, w_a, w_b, c_a, c_b, eps):
+        """float32 [T, C]: c_a a + c_b b, or with weights c_a a / rms(a) * w_a + c_b b / rms(b) * w_b."""
+        A = self.acc
+        aa, ba = a.to(A), b.to(A)
+        if w_a is not None:
+            aa = aa * torch.rsqrt((aa * aa).mean(-1, keepdim=True) + eps) * w_a.to(A)
+            ba = ba * torch.rsqrt((ba * ba).mean(-1, keepdim=True) + eps) * w_b.to(A)
+        return (c_a * aa + c_b * ba).to(torch.float32)
+
+    def residual_add_vectors(self, x, a, s_a, b=None, s_b=None, b2=None):
+        """x += s_a * a + s_b * (b + b2), element by element along a row (a vector None: ones; b, b2 may be None)."""
+        A = self.acc
+        total = a.to(A) if s_a is None else a.to(A) * s_a.to(A)
+        if b is not None:
+            bb = b.to(A) if b2 is None else b.to(A) + b2.to(A)
+            total = total + (bb if s_b is None else bb * s_b.to(A))
+        x += total.to(torch.float32)
+
     # ------------------------------------------------------- mixture of experts
-    def moe_route(self, z, correction, top, of_chosen=False):
+    def moe_route(self, z, correction, top, of_chosen=False, kind=None, floor=0.0):
+        if kind == "sigmoid_normalized":                    # sigmoid scores; the chosen scores over their sum
+            s = torch.sigmoid(z.to(self.acc))
+            choice = s if correction is None else s + correction.to(self.acc)
+            ids = torch.topk(choice, top, dim=-1).indices
+            w = torch.gather(s, 1, ids)
+            return ids.to(torch.int32), (w / (w.sum(-1, keepdim=True) + floor)).to(torch.float32)
         if of_chosen:                                       # the largest logits; softmax among them alone
             za = z.to(self.acc) if correction is None else z.to(self.acc) + correction.to(self.acc)
             best = torch.topk(za, top, dim=-1)
@@ -317,8 +436,8 @@ class PlainKernels:
         return ids.to(torch.int32), torch.gather(s, 1, ids).to(torch.float32)
 
     def moe_experts(self, h, w_up, w_down, ids, weights, experts, out_dtype, glu=None):
-        """`glu` = (limit, slope): w_up holds an expert's gate rows above its up rows, and the activation is
-        g sigmoid(slope g) (u + 1) with g = min(gate, limit), u = clamp(up, -limit, limit)."""
+        """`glu` = (limit, slope[, offset = 1]): w_up holds an expert's gate rows above its up rows, and the activation is
+        g sigmoid(slope g) (u + offset) with g = min(gate, limit), u = clamp(up, -limit, limit)."""
         ha = h.to(self.acc)
         out = torch.zeros_like(ha)
         for t in range(h.shape[0]):
@@ -329,7 +448,7 @@ class PlainKernels:
                     both = w_up[e].to(self.acc) @ ha[t]
                     ff = both.shape[0] // 2
                     gate, up = torch.clamp(both[:ff], max=glu[0]), torch.clamp(both[ff:], min=-glu[0], max=glu[0])
-                    a = gate * torch.sigmoid(glu[1] * gate) * (up + 1.0)
+                    a = gate * torch.sigmoid(glu[1] * gate) * (up + (glu[2] if len(glu) > 2 else 1.0))
                     out[t] += wgt * (w_down[e].to(self.acc) @ a.to(h.dtype).to(self.acc))
                 else:
                     a = torch.relu(w_up[e].to(self.acc) @ ha[t]) ** 2
