@@ -68,7 +68,7 @@ __global__ void attention_generic_kernel(const T* __restrict__ q, const T* __res
                                          const int* __restrict__ rows, T* __restrict__ out, int num_tokens, int nq,
                                          int nkv, int d, int d_v, int d_row,
                                          int page_size, int max_blocks, int num_pages, int window, int chunk,
-                                         int sink, float scale) {
+                                         int sink, const float* __restrict__ sink_values, float scale) {
   __shared__ __align__(16) float q_s[kWarpsPerBlock][kMaxHeadDim];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const long long item = (long long)blockIdx.x * kWarpsPerBlock + warp;
@@ -90,7 +90,8 @@ __global__ void attention_generic_kernel(const T* __restrict__ q, const T* __res
   if (chunk > 0) first = max(first, (pos / chunk) * chunk);
   const int end = pos + 1;
   // the sink is a key of score 0 that comes first and brings no value: maximum 0, sum 1
-  float m = sink ? 0.0f : -INFINITY, l = sink ? 1.0f : 0.0f;
+  // (with sink_values the score is the head's learned number instead of 0)
+  float m = sink ? (sink_values ? sink_values[h] : 0.0f) : -INFINITY, l = sink ? 1.0f : 0.0f;
   float acc[kMaxHeadDim / 32];
 #pragma unroll
   for (int i = 0; i < kMaxHeadDim / 32; ++i) acc[i] = 0.0f;
@@ -140,11 +141,11 @@ __global__ void attention_generic_kernel(const T* __restrict__ q, const T* __res
 
 using namespace ifx;
 
-extern "C" int ifx_attention_generic_ex(const void* q, const void* kv_pool, const int* block_table,
-                                        const int* positions, const int* token_req, const int* req_slot,
-                                        const int* rows, void* out, int num_tokens, int nq, int nkv, int d, int d_v,
-                                        int d_row, int page_size, int max_blocks, int num_pages, int window, int chunk,
-                                        int sink, float scale, int dtype, cudaStream_t stream) {
+extern "C" int ifx_attention_generic_sink(const void* q, const void* kv_pool, const int* block_table,
+                                          const int* positions, const int* token_req, const int* req_slot,
+                                          const int* rows, void* out, int num_tokens, int nq, int nkv, int d, int d_v,
+                                          int d_row, int page_size, int max_blocks, int num_pages, int window, int chunk,
+                                          int sink, const float* sink_values, float scale, int dtype, cudaStream_t stream) {
   if (num_tokens <= 0) return 0;
   if (nq <= 0 || nkv <= 0 || nq % nkv || d <= 0 || d_v <= 0 || d_row % 8 || d_row > kMaxHeadDim || d > d_row ||
       d_v > d_row || page_size <= 0 || max_blocks <= 0 || chunk < 0)
@@ -154,16 +155,26 @@ extern "C" int ifx_attention_generic_ex(const void* q, const void* kv_pool, cons
   if (dtype == IFX_DT_F32)
     attention_generic_kernel<float><<<blocks, kWarpsPerBlock * 32, 0, stream>>>(
         (const float*)q, (const float*)kv_pool, block_table, positions, token_req, req_slot, rows, (float*)out,
-        num_tokens, nq, nkv, d, d_v, d_row, page_size, max_blocks, num_pages, window, chunk, sink, scale);
+        num_tokens, nq, nkv, d, d_v, d_row, page_size, max_blocks, num_pages, window, chunk, sink, sink_values, scale);
   else if (dtype == IFX_DT_BF16)
     attention_generic_kernel<__nv_bfloat16><<<blocks, kWarpsPerBlock * 32, 0, stream>>>(
         (const __nv_bfloat16*)q, (const __nv_bfloat16*)kv_pool, block_table, positions, token_req, req_slot,
         rows, (__nv_bfloat16*)out, num_tokens, nq, nkv, d, d_v, d_row, page_size, max_blocks, num_pages, window,
-        chunk, sink, scale);
+        chunk, sink, sink_values, scale);
   else
     return IFX_E_DTYPE;
   IFX_CHECK_LAUNCH();
   return 0;
+}
+
+extern "C" int ifx_attention_generic_ex(const void* q, const void* kv_pool, const int* block_table,
+                                        const int* positions, const int* token_req, const int* req_slot,
+                                        const int* rows, void* out, int num_tokens, int nq, int nkv, int d, int d_v,
+                                        int d_row, int page_size, int max_blocks, int num_pages, int window, int chunk,
+                                        int sink, float scale, int dtype, cudaStream_t stream) {
+  return ifx_attention_generic_sink(q, kv_pool, block_table, positions, token_req, req_slot, rows, out, num_tokens, nq, nkv,
+                                    d, d_v, d_row, page_size, max_blocks, num_pages, window, chunk, sink, nullptr, scale, dtype,
+                                    stream);
 }
 
 extern "C" int ifx_attention_generic(const void* q, const void* kv_pool, const int* block_table,

@@ -72,7 +72,7 @@ __global__ void __launch_bounds__(192, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                     __nv_bfloat16* __restrict__ out, int M, int N, int K, int up_row_offset, int m_tiles, int n_tiles,
                     int* __restrict__ error_flag, const int* __restrict__ tile_group, int group_rows,
-                    const float* __restrict__ row_scale, float glu_limit, float glu_slope) {
+                    const float* __restrict__ row_scale, float glu_limit, float glu_slope, float glu_offset) {
   constexpr bool PAIRED = MODE == GEMM_SWIGLU || MODE == GEMM_GROUP_GLU;   // a tile is 128 gate rows and their 128 up rows
   constexpr int OUT_COLS = PAIRED ? kBN / 2 : kBN;                  // output columns a tile makes
   constexpr bool GROUPED = MODE == GEMM_GROUP_RELU2 || MODE == GEMM_GROUP_SCALE || MODE == GEMM_GROUP_GLU;
@@ -207,7 +207,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
           if (MODE == GEMM_GROUP_GLU) {                               // g sigmoid(slope g) (u + 1), g cut from above, u on both sides
             const float gate = fminf(v[j], glu_limit);
             const float up = fminf(fmaxf(__uint_as_float(u[j]), -glu_limit), glu_limit);
-            v[j] = __fdividef(gate, 1.0f + __expf(-glu_slope * gate)) * (up + 1.0f);
+            v[j] = __fdividef(gate, 1.0f + __expf(-glu_slope * gate)) * (up + glu_offset);
           }
           if (MODE == GEMM_GROUP_RELU2) v[j] = fmaxf(v[j], 0.0f) * fmaxf(v[j], 0.0f);
           if (MODE == GEMM_GROUP_SCALE) v[j] *= factor;
@@ -262,7 +262,7 @@ static int gemm_sm_count() {
 template <int MODE>
 static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mw, void* out, int M, int N, int K, int up_row_offset,
                        int* error_flag, cudaStream_t stream, const int* tile_group = nullptr, int group_rows = 0,
-                       const float* row_scale = nullptr, float glu_limit = 0.0f, float glu_slope = 0.0f) {
+                       const float* row_scale = nullptr, float glu_limit = 0.0f, float glu_slope = 0.0f, float glu_offset = 1.0f) {
   constexpr int OUT_COLS = (MODE == GEMM_SWIGLU || MODE == GEMM_GROUP_GLU) ? kBN / 2 : kBN;
   const size_t smem = 1024 + (size_t)kGemmStages * kStageBytes + (2 * kGemmStages + 4) * 8 + 16;
   static bool configured = false;
@@ -276,7 +276,7 @@ static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mw, void* out, 
   const int grid = tiles < gemm_sm_count() ? tiles : gemm_sm_count();
   gemm_tcgen05_kernel<MODE><<<grid, 192, smem, stream>>>(ma, mw, reinterpret_cast<__nv_bfloat16*>(out), M, N, K,
                                                          up_row_offset, m_tiles, n_tiles, error_flag, tile_group,
-                                                         group_rows, row_scale, glu_limit, glu_slope);
+                                                         group_rows, row_scale, glu_limit, glu_slope, glu_offset);
   IFX_CHECK_LAUNCH();
   return 0;
 }
@@ -329,10 +329,10 @@ extern "C" int ifx_gemm_tcgen05_grouped(const void* act, const void* W, void* ou
 }
 
 // The gated form of the same: W [groups * 2 ff, K], a group's ff gate rows above its ff up rows; out [M, ff] bfloat16 =
-// g sigmoid(slope g) (u + 1) with g = min(act . gate^T, limit), u = clamp(act . up^T, -limit, limit).
-extern "C" int ifx_gemm_tcgen05_grouped_glu(const void* act, const void* W, void* out, int M, int ff, int K, int groups,
-                                            const int* tile_group, float limit, float slope, int* error_flag,
-                                            cudaStream_t stream) {
+// g sigmoid(slope g) (u + offset) with g = min(act . gate^T, limit), u = clamp(act . up^T, -limit, limit).
+extern "C" int ifx_gemm_tcgen05_grouped_glu_offset(const void* act, const void* W, void* out, int M, int ff, int K, int groups,
+                                                   const int* tile_group, float limit, float slope, float offset,
+                                                   int* error_flag, cudaStream_t stream) {
   if (M <= 0 || ff <= 0) return 0;
   if (K <= 0 || K % 8 || M % kBM || groups <= 0 || error_flag == nullptr || out == nullptr || tile_group == nullptr)
     return IFX_E_BADARG;
@@ -341,5 +341,12 @@ extern "C" int ifx_gemm_tcgen05_grouped_glu(const void* act, const void* W, void
   if (rc) return rc;
   rc = make_tensor_map_bf16(&ma, act, M, K, kBM);
   if (rc) return rc;
-  return launch_gemm<GEMM_GROUP_GLU>(ma, mw, out, M, ff, K, ff, error_flag, stream, tile_group, 2 * ff, nullptr, limit, slope);
+  return launch_gemm<GEMM_GROUP_GLU>(ma, mw, out, M, ff, K, ff, error_flag, stream, tile_group, 2 * ff, nullptr, limit, slope,
+                                     offset);
+}
+
+extern "C" int ifx_gemm_tcgen05_grouped_glu(const void* act, const void* W, void* out, int M, int ff, int K, int groups,
+                                            const int* tile_group, float limit, float slope, int* error_flag,
+                                            cudaStream_t stream) {
+  return ifx_gemm_tcgen05_grouped_glu_offset(act, W, out, M, ff, K, groups, tile_group, limit, slope, 1.0f, error_flag, stream);
 }

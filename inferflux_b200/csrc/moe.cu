@@ -3,11 +3,12 @@
 //   moe_route     scores = softmax(z) over all router outputs (float32); the `top` largest of score + correction
 //                 are chosen (the earlier index wins a tie); their weights are the scores themselves
 //                 (of_chosen: the `top` largest of z + correction are chosen and the weights are the softmax over
-//                 the chosen z alone)
+//                 the chosen z alone; sigmoid: scores = sigmoid(z), the `top` largest of score + correction are chosen,
+//                 and the weights are the chosen scores divided by (their sum + floor))
 //   moe_up        act[p] = relu(W_up[e] h[t])^2 for every (token, choice) pair p = t * top + c whose expert e
 //                 has weights (experts numbered from `experts` on hand their input on unchanged); or, gated (an
 //                 expert's gate rows above its up rows, [experts, 2 ff, width]), with g = min(gate, limit) and
-//                 u = clamp(up, -limit, limit): act[p] = g sigmoid(slope g) (u + 1)
+//                 u = clamp(up, -limit, limit): act[p] = g sigmoid(slope g) (u + offset)
 //   moe_down      out[t] = sum over the token's choices, in their order, of weight * (W_down[e] act[p]), or
 //                 weight * h[t] for an expert without weights
 //
@@ -30,14 +31,16 @@ namespace ifx {
 constexpr int kMaxRouterOutputs = 1024;
 
 __global__ void moe_route_kernel(const float* __restrict__ z, const float* __restrict__ correction,
-                                 int* __restrict__ ids, float* __restrict__ weights, int T, int n, int top, int of_chosen) {
+                                 int* __restrict__ ids, float* __restrict__ weights, int T, int n, int top, int of_chosen,
+                                 float floor) {
+  const bool sigmoid = of_chosen == 2;
   __shared__ float score_s[4][kMaxRouterOutputs];
   __shared__ float choice_s[4][kMaxRouterOutputs];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int t = blockIdx.x * 4 + warp;
   if (t >= T) return;
   const float* zr = z + (size_t)t * n;
-  if (of_chosen) {
+  if (of_chosen == 1) {
     for (int i = lane; i < n; i += 32) {
       score_s[warp][i] = zr[i];
       choice_s[warp][i] = zr[i] + (correction ? correction[i] : 0.0f);
@@ -81,11 +84,11 @@ __global__ void moe_route_kernel(const float* __restrict__ z, const float* __res
   m = warp_max(m);
   float sum = 0.0f;
   for (int i = lane; i < n; i += 32) {
-    const float e = expf(zr[i] - m);
+    const float e = sigmoid ? 1.0f / (1.0f + expf(-zr[i])) : expf(zr[i] - m);
     score_s[warp][i] = e;
     sum += e;
   }
-  sum = warp_sum(sum);
+  sum = sigmoid ? 1.0f : warp_sum(sum);
   for (int i = lane; i < n; i += 32) {
     const float sc = score_s[warp][i] / sum;
     score_s[warp][i] = sc;
@@ -112,6 +115,12 @@ __global__ void moe_route_kernel(const float* __restrict__ z, const float* __res
       choice_s[warp][at] = -INFINITY;
     }
     __syncwarp();
+  }
+  if (sigmoid && lane == 0) {                            // the chosen scores over their sum, added in the order of the choice
+    float total = 0.0f;
+    for (int c = 0; c < top; ++c) total += weights[(size_t)t * top + c];
+    total += floor;
+    for (int c = 0; c < top; ++c) weights[(size_t)t * top + c] /= total;
   }
 }
 
@@ -214,7 +223,7 @@ constexpr int kMoeWarps = 8;
 template <typename T, bool GLU>
 __global__ void moe_up_kernel(const T* __restrict__ h, const T* __restrict__ w_up, const int* __restrict__ ids,
                               T* __restrict__ act, int top, int experts, int width, int ff, int rows_per_block,
-                              float limit, float slope) {
+                              float limit, float slope, float offset) {
   extern __shared__ __align__(16) float h_s[];
   const int p = blockIdx.x;
   const int e = ids[p];
@@ -242,7 +251,7 @@ __global__ void moe_up_kernel(const T* __restrict__ h, const T* __restrict__ w_u
         for (int r = 0; r < 4; ++r) {
           const float g = fminf(z[r], limit), u = fminf(fmaxf(up[r], -limit), limit);
           if (f + r * kMoeWarps <= last)
-            act[(size_t)p * ff + f + r * kMoeWarps] = from_f32<T>(g / (1.0f + expf(-slope * g)) * (u + 1.0f));
+            act[(size_t)p * ff + f + r * kMoeWarps] = from_f32<T>(g / (1.0f + expf(-slope * g)) * (u + offset));
         }
       }
       continue;
@@ -381,14 +390,20 @@ using namespace ifx;
 
 extern "C" {
 
-int ifx_moe_route_ex(const float* z, const float* correction, int* ids, float* weights, int T, int n, int top,
-                     int of_chosen, cudaStream_t stream) {
+// kind: 0 softmax over all, 1 softmax over the chosen, 2 sigmoid scores over the chosen scores' sum + floor.
+int ifx_moe_route_kind(const float* z, const float* correction, int* ids, float* weights, int T, int n, int top,
+                       int kind, float floor, cudaStream_t stream) {
   if (T <= 0) return 0;
-  if (n <= 0 || top <= 0 || top > n) return IFX_E_BADARG;
+  if (n <= 0 || top <= 0 || top > n || kind < 0 || kind > 2) return IFX_E_BADARG;
   if (n > kMaxRouterOutputs) return IFX_E_TOOBIG;
-  moe_route_kernel<<<(T + 3) / 4, 128, 0, stream>>>(z, correction, ids, weights, T, n, top, of_chosen);
+  moe_route_kernel<<<(T + 3) / 4, 128, 0, stream>>>(z, correction, ids, weights, T, n, top, kind, floor);
   IFX_CHECK_LAUNCH();
   return 0;
+}
+
+int ifx_moe_route_ex(const float* z, const float* correction, int* ids, float* weights, int T, int n, int top,
+                     int of_chosen, cudaStream_t stream) {
+  return ifx_moe_route_kind(z, correction, ids, weights, T, n, top, of_chosen ? 1 : 0, 0.0f, stream);
 }
 
 int ifx_moe_route(const float* z, const float* correction, int* ids, float* weights, int T, int n, int top,
@@ -400,6 +415,9 @@ int ifx_moe_route(const float* z, const float* correction, int* ids, float* weig
 int ifx_moe_experts_ex(const void* h, const void* w_up, const void* w_down, const int* ids, const float* weights,
                        void* act, void* out, int T, int top, int experts, int width, int ff, int dtype, int out_dtype,
                        int glu, float limit, float slope, cudaStream_t stream);
+int ifx_moe_experts_glu(const void* h, const void* w_up, const void* w_down, const int* ids, const float* weights,
+                        void* act, void* out, int T, int top, int experts, int width, int ff, int dtype, int out_dtype,
+                        int glu, float limit, float slope, float offset, cudaStream_t stream);
 
 int ifx_moe_experts(const void* h, const void* w_up, const void* w_down, const int* ids, const float* weights,
                     void* act, void* out, int T, int top, int experts, int width, int ff, int dtype, int out_dtype,
@@ -408,10 +426,18 @@ int ifx_moe_experts(const void* h, const void* w_up, const void* w_down, const i
                             0.0f, stream);
 }
 
-// glu: w_up is [experts, 2 ff, width], an expert's gate rows above its up rows, and the activation is the clamped gated one.
 int ifx_moe_experts_ex(const void* h, const void* w_up, const void* w_down, const int* ids, const float* weights,
                        void* act, void* out, int T, int top, int experts, int width, int ff, int dtype, int out_dtype,
                        int glu, float limit, float slope, cudaStream_t stream) {
+  return ifx_moe_experts_glu(h, w_up, w_down, ids, weights, act, out, T, top, experts, width, ff, dtype, out_dtype, glu, limit,
+                             slope, 1.0f, stream);
+}
+
+// glu: w_up is [experts, 2 ff, width], an expert's gate rows above its up rows, and the activation is the gated one,
+// g sigmoid(slope g) (u + offset) with g cut at limit from above and u on both sides (limit +inf: nothing is cut).
+int ifx_moe_experts_glu(const void* h, const void* w_up, const void* w_down, const int* ids, const float* weights,
+                        void* act, void* out, int T, int top, int experts, int width, int ff, int dtype, int out_dtype,
+                        int glu, float limit, float slope, float offset, cudaStream_t stream) {
   if (T <= 0) return 0;
   if (top <= 0 || experts < 0 || width <= 0 || ff <= 0) return IFX_E_BADARG;
   if ((size_t)width * 4 > 160 * 1024 || (size_t)ff * 4 > 160 * 1024) return IFX_E_TOOBIG;
@@ -424,7 +450,7 @@ int ifx_moe_experts_ex(const void* h, const void* w_up, const void* w_down, cons
       auto up = glu ? moe_up_kernel<TT, true> : moe_up_kernel<TT, false>;                                         \
       if (smem_up > 48 * 1024) cudaFuncSetAttribute(up, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_up); \
       up<<<grid_up, kMoeWarps * 32, smem_up, stream>>>((const TT*)h, (const TT*)w_up, ids, (TT*)act, top, experts, \
-                                                       width, ff, up_rows, limit, slope);                         \
+                                                       width, ff, up_rows, limit, slope, offset);                         \
     }                                                                                                             \
     auto down = moe_down_kernel<TT, TO>;                                                                          \
     if (smem_down > 48 * 1024)                                                                                    \

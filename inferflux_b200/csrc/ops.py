@@ -159,7 +159,10 @@ class CudaKernels:
                    "ifx_moe_gather", "ifx_moe_combine", "ifx_gemm_tcgen05_grouped", "ifx_attention_prefill_tcgen05_ex",
                    "ifx_groupnorm_stream", "ifx_residual_add_scaled", "ifx_gelu_mul_table", "ifx_embed_scaled", "ifx_scale_f32",
                    "ifx_delta_rule_scan", "ifx_latent_rope_append", "ifx_latent_attention_generic_rot", "ifx_moe_route_ex",
-                   "ifx_moe_experts_ex", "ifx_gemm_tcgen05_grouped_glu", "ifx_latent_attention_mma_rot", "ifx_latent_attention_mma_supports_rot"):
+                   "ifx_moe_experts_ex", "ifx_gemm_tcgen05_grouped_glu", "ifx_latent_attention_mma_rot", "ifx_latent_attention_mma_supports_rot",
+                   "ifx_moe_route_kind", "ifx_moe_experts_glu", "ifx_gemm_tcgen05_grouped_glu_offset", "ifx_norm_rope_append_ex",
+                   "ifx_attention_generic_sink", "ifx_short_conv_ex", "ifx_decay_scan", "ifx_decay_scan_split", "ifx_bigram_add",
+                   "ifx_rmsnorm_pair", "ifx_gate_mul", "ifx_gated_groupnorm", "ifx_pair_combine", "ifx_residual_add_vectors"):
             getattr(self.lib, fn).restype = ctypes.c_int
         self.lib.ifx_delta_rule_scratch_floats.restype = ctypes.c_longlong
         self.lib.ifx_sample_scratch_bytes.restype = ctypes.c_longlong
@@ -649,14 +652,17 @@ class CudaKernels:
         return int(extra_len.get("attn.prefill_tiles", 0) == 0 and extra_len["attn.decode_rows"] * nkv * 8 <= 148)
 
     def rope_append(self, qkv, bias, rotary, nq, nkv, d, ctx, cache, q_norm=None, k_norm=None, norm_eps=0.0, dv=None,
-                    own_kv=True):
+                    own_kv=True, q_temp=None):
         """`qkv`: the stacked projections [T, (nq + 2 nkv) d] as a tensor or a PartialSum.
         With `q_norm` / `k_norm` (float32 [d]) every query / key head is RMS-normed with that weight before the
         rotation; `dv`: the values' head size if it is not `d` (cache rows hold the larger of the two);
-        `own_kv` False: the rows hold queries only and nothing is stored."""
-        if q_norm is not None or k_norm is not None or (dv is not None and dv != d) or not own_kv:
+        `own_kv` False: the rows hold queries only and nothing is stored; `q_temp` = (coef, every): the queries are
+        multiplied by 1 + coef ln(floor((p + 1) / every) + 1) at position p.  A table whose cos and sin are made longer
+        (`rotary.magnitude`) takes the general kernel too."""
+        if (q_norm is not None or k_norm is not None or (dv is not None and dv != d) or not own_kv or q_temp is not None
+                or (rotary is not None and rotary.magnitude != 1.0)):
             return self._norm_rope_append(qkv, bias, rotary, nq, nkv, d, ctx, cache, q_norm, k_norm, norm_eps,
-                                          d if dv is None else dv, own_kv)
+                                          d if dv is None else dv, own_kv, q_temp)
         partial, splits = None, 0
         if isinstance(qkv, PartialSum):
             partial, splits, dtype, device = qkv.parts, qkv.splits, qkv.dtype, qkv.parts.device
@@ -683,7 +689,7 @@ class CudaKernels:
         self.launches += 1
         return q_out
 
-    def _norm_rope_append(self, qkv, bias, rotary, nq, nkv, d, ctx, cache, q_norm, k_norm, norm_eps, dv, own_kv):
+    def _norm_rope_append(self, qkv, bias, rotary, nq, nkv, d, ctx, cache, q_norm, k_norm, norm_eps, dv, own_kv, q_temp=None):
         _need(bias is None, "rope_append: biases and head norms together are not built")
         partial, splits = None, 0
         if isinstance(qkv, PartialSum):
@@ -707,13 +713,15 @@ class CudaKernels:
             _need(kv.shape[1] == 2 and kv.shape[2] == nkv and d_row >= max(d, dv), "rope_append: the cache does not fit the heads")
         rot = 0 if rotary is None else int(rotary.rotary_dim)
         _need(rot <= d, "rope_append: rotary_dim exceeds the head size")
-        _check(self.lib.ifx_norm_rope_append(
+        _check(self.lib.ifx_norm_rope_append_ex(
             _ptr(qkv), _ptr(partial), splits, _ptr(q_norm), _ptr(k_norm), ctypes.c_float(norm_eps),
             _ptr(None if rotary is None else rotary.inv_freq), rot,
             int(bool(rotary.interleaved)) if rotary is not None else 0, _ptr(ctx.positions), _ptr(ctx.token_req),
             _ptr(ctx.req_slot), _ptr(table), 0 if table is None else table.shape[1], cache.page_size,
             0 if kv is None else kv.shape[0], _ptr(kv if write else None), _ptr(q_out), T, nq, src_kv, nkv, d, dv, d_row,
-            int(write), _DT[dtype], _stream()), "rope_append (normed heads)")
+            int(write), ctypes.c_float(1.0 if rotary is None else rotary.magnitude),
+            ctypes.c_float(0.0 if q_temp is None else q_temp[0]), 0 if q_temp is None else int(q_temp[1]),
+            _DT[dtype], _stream()), "rope_append (normed heads)")
         self.launches += 1
         return q_out
 
@@ -723,8 +731,9 @@ class CudaKernels:
         whose additions depend on the position only.  bfloat16: the tiled kernels,
         one launch for the prompt portions and one for the single decoded tokens.
         `chunk`: a query at position p sees keys from (p // chunk) * chunk on; `sink`: one more unit in the
-        softmax's denominator; `dv`: the values' head size if it is not `d`."""
-        if chunk or sink or (dv is not None and dv != d):
+        softmax's denominator (True), or exp of a learned number per head (a float32 tensor [nq]); `dv`: the values'
+        head size if it is not `d`."""
+        if chunk or torch.is_tensor(sink) or sink or (dv is not None and dv != d):
             return self._attention_masked(q, nq, nkv, d, d if dv is None else dv, window, chunk, sink, scale, ctx, cache)
         T = q.shape[0]
         kv, table = cache.kv, cache.block_table
@@ -798,7 +807,11 @@ class CudaKernels:
               "attention: the cache does not fit the heads")
         out = torch.empty((T, nq * dv), dtype=q.dtype, device=q.device)
         win = 0 if window is None else int(window)
-        if (q.dtype == torch.bfloat16 and d == dv == d_row and nq // nkv <= 16 and self.lib.ifx_attention_mma_supports(d)
+        sink_values = sink if torch.is_tensor(sink) else None
+        if sink_values is not None:
+            _need(sink_values.dtype == torch.float32 and sink_values.numel() == nq and sink_values.is_contiguous(),
+                  "attention: the learned sink is float32 [heads]")
+        if (sink_values is None and q.dtype == torch.bfloat16 and d == dv == d_row and nq // nkv <= 16 and self.lib.ifx_attention_mma_supports(d)
                 and os.environ.get("INFERFLUX_B200_MASKED_TILES", "1") != "0"):
             # the tiled kernels: prompt portions on mma.sync tiles, single tokens on the cluster kernel
             if "attn.prefill_tiles" not in ctx.extra:          # a step context built without the mixer as a provider
@@ -832,11 +845,11 @@ class CudaKernels:
                     splits, max_keys, _ptr(self.error_flag), _stream()), "attention (masked, decoded tokens)")
                 self.launches += 1
             return out
-        _check(self.lib.ifx_attention_generic_ex(
+        _check(self.lib.ifx_attention_generic_sink(
             _ptr(q), _ptr(kv), _ptr(table), _ptr(ctx.positions), _ptr(ctx.token_req), _ptr(ctx.req_slot), _ptr(None),
             _ptr(out), T, nq, nkv, d, dv, d_row, cache.page_size, table.shape[1], kv.shape[0],
-            0 if window is None else int(window), int(chunk or 0), int(bool(sink)), ctypes.c_float(scale), _DT[q.dtype],
-            _stream()), "attention (masked)")
+            0 if window is None else int(window), int(chunk or 0), int(sink_values is not None or bool(sink)),
+            _ptr(sink_values), ctypes.c_float(scale), _DT[q.dtype], _stream()), "attention (masked)")
         self.launches += 1
         return out
 
@@ -1004,11 +1017,16 @@ class CudaKernels:
                "softcap")
         self.launches += 1
 
-    def short_conv(self, h, w, taps, state, index, ctx):
+    def short_conv(self, h, w, taps, state, index, ctx, add_input=True, bias=None, act=None, columns=None):
         """h + causal depthwise convolution of h over each request's tokens; `state[:, index]` (float32
-        [slots, convolutions, taps - 1, channels]) brings the inputs before the step and takes the last ones."""
-        T, C = h.shape
-        _need(h.is_contiguous() and w.dtype == torch.float32 and tuple(w.shape) == (C, taps), "short_conv: bad operands")
+        [slots, convolutions, taps - 1, channels]) brings the inputs before the step and takes the last ones.
+        `add_input` False: the convolution alone; `bias` (float32 [channels]) is added and `act` ("silu") applied
+        behind it; `columns` = (first, count): the convolution runs over those columns of `h` and returns them alone."""
+        T, width = h.shape
+        col0, C = (0, width) if columns is None else (int(columns[0]), int(columns[1]))
+        _need(h.is_contiguous() and w.dtype == torch.float32 and tuple(w.shape) == (C, taps) and w.is_contiguous()
+              and 0 <= col0 and col0 + C <= width and act in (None, "silu")
+              and (bias is None or (bias.dtype == torch.float32 and bias.numel() == C)), "short_conv: bad operands")
         st_ptr, stride = ctypes.c_void_p(0), 0
         if taps > 1:
             _need(state is not None and state.dtype == torch.float32 and tuple(state.shape[2:]) == (taps - 1, C)
@@ -1016,10 +1034,12 @@ class CudaKernels:
                   "short_conv: the state does not fit the convolution")
             stride = state.stride(0)                       # a slot's rows may be part of a longer state row
             st_ptr = ctypes.c_void_p(state.data_ptr() + 4 * index * state.stride(1))
-        out = torch.empty_like(h)
-        _check(self.lib.ifx_short_conv(_ptr(h), _ptr(w), st_ptr, ctypes.c_longlong(stride), _ptr(ctx.token_req),
-                                       _ptr(ctx.req_slot), _ptr(ctx.cu_seqlens), _ptr(out), T, ctx.num_requests, C,
-                                       taps, int(ctx.max_span > 1), _DT[h.dtype], _stream()), "short_conv")
+        out = torch.empty((T, C), dtype=h.dtype, device=h.device)
+        _check(self.lib.ifx_short_conv_ex(ctypes.c_void_p(h.data_ptr() + col0 * h.element_size()), ctypes.c_longlong(width),
+                                          _ptr(w), _ptr(bias), st_ptr, ctypes.c_longlong(stride), _ptr(ctx.token_req),
+                                          _ptr(ctx.req_slot), _ptr(ctx.cu_seqlens), _ptr(out), T, ctx.num_requests, C,
+                                          taps, int(ctx.max_span > 1), ctypes.c_float(1.0 if add_input else 0.0),
+                                          int(act == "silu"), _DT[h.dtype], _stream()), "short_conv")
         self.launches += 1 + int(taps > 1 and ctx.max_span > 1)
         return out
 
@@ -1272,17 +1292,21 @@ class CudaKernels:
         return y
 
     # ------------------------------------------------------- mixture of experts
-    def moe_route(self, z, correction, top, of_chosen=False):
+    def moe_route(self, z, correction, top, of_chosen=False, kind=None, floor=0.0):
         """(ids int32 [T, top], weights float32 [T, top]) from router logits z float32 [T, n]: softmax scores; the
         `top` largest of score + correction are chosen, their weights are the scores.  `of_chosen`: the `top`
-        largest of z + correction are chosen, and the weights are the softmax over the chosen logits alone."""
+        largest of z + correction are chosen, and the weights are the softmax over the chosen logits alone.
+        `kind` = "sigmoid_normalized": scores = sigmoid(z), the `top` largest of score + correction are chosen, and the
+        weights are the chosen scores divided by (their sum + floor)."""
+        _need(kind in (None, "sigmoid_normalized"), f"moe_route: unknown kind {kind!r}")
         T, n = z.shape
         _need(z.dtype == torch.float32 and z.is_contiguous() and (correction is None or (correction.dtype == torch.float32
               and correction.numel() == n)), "moe_route: float32 logits and corrections")
         ids = torch.empty((T, top), dtype=torch.int32, device=z.device)
         weights = torch.empty((T, top), dtype=torch.float32, device=z.device)
-        _check(self.lib.ifx_moe_route_ex(_ptr(z), _ptr(correction), _ptr(ids), _ptr(weights), T, n, int(top), int(bool(of_chosen)),
-                                         _stream()), "moe_route")
+        _check(self.lib.ifx_moe_route_kind(_ptr(z), _ptr(correction), _ptr(ids), _ptr(weights), T, n, int(top),
+                                           2 if kind == "sigmoid_normalized" else int(bool(of_chosen)), ctypes.c_float(floor),
+                                           _stream()), "moe_route")
         self.launches += 1
         return ids, weights
 
@@ -1290,9 +1314,12 @@ class CudaKernels:
         """sum over a token's choices of weight * W_down[e] relu(W_up[e] h)^2, or weight * h for e >= experts.
         w_up [experts, ff, width], w_down [experts, width, ff] in h's dtype.  `glu` = (limit, slope): w_up is
         [experts, 2 ff, width], an expert's gate rows above its up rows, and the activation is
-        g sigmoid(slope g) (u + 1) with g = min(gate, limit), u = clamp(up, -limit, limit)."""
+        g sigmoid(slope g) (u + 1) with g = min(gate, limit), u = clamp(up, -limit, limit); a third number replaces
+        the 1 (limit inf, slope 1 and 0 give silu(gate) * up)."""
         T, width = h.shape
         top = ids.shape[1]
+        if glu is not None and len(glu) == 2:
+            glu = (glu[0], glu[1], 1.0)
         if glu is not None:
             _need(experts > 0 and w_up.shape[1] % 2 == 0, "moe_experts: gated experts need gate and up rows")
             ff = w_up.shape[1] // 2
@@ -1304,9 +1331,10 @@ class CudaKernels:
                 return self._moe_experts_tiles(h, w_up, w_down, ids, weights, experts, out_dtype, glu=glu)
             act = torch.empty((T * top, ff), dtype=h.dtype, device=h.device)
             out = torch.empty((T, width), dtype=out_dtype, device=h.device)
-            _check(self.lib.ifx_moe_experts_ex(_ptr(h), _ptr(w_up), _ptr(w_down), _ptr(ids), _ptr(weights), _ptr(act), _ptr(out),
-                                               T, top, int(experts), width, ff, _DT[h.dtype], _DT[out_dtype], 1,
-                                               ctypes.c_float(glu[0]), ctypes.c_float(glu[1]), _stream()), "moe_experts (gated)")
+            _check(self.lib.ifx_moe_experts_glu(_ptr(h), _ptr(w_up), _ptr(w_down), _ptr(ids), _ptr(weights), _ptr(act), _ptr(out),
+                                                T, top, int(experts), width, ff, _DT[h.dtype], _DT[out_dtype], 1,
+                                                ctypes.c_float(glu[0]), ctypes.c_float(glu[1]), ctypes.c_float(glu[2]),
+                                                _stream()), "moe_experts (gated)")
             self.launches += 2
             return out
         ff = w_up.shape[1] if experts else 1
@@ -1346,9 +1374,10 @@ class CudaKernels:
         _check(self.lib.ifx_moe_gather(_ptr(h), _ptr(row_pair), _ptr(rows), cap, top, width, _stream()), "moe_gather")
         act = torch.empty((cap, ff), dtype=torch.bfloat16, device=dev)
         if glu is not None:
-            _check(self.lib.ifx_gemm_tcgen05_grouped_glu(_ptr(rows), _ptr(w_up), _ptr(act), cap, ff, width, int(experts),
-                                                         _ptr(tile_group), ctypes.c_float(glu[0]), ctypes.c_float(glu[1]),
-                                                         _ptr(self.error_flag), _stream()), "moe experts (gate and up, tiles)")
+            _check(self.lib.ifx_gemm_tcgen05_grouped_glu_offset(
+                _ptr(rows), _ptr(w_up), _ptr(act), cap, ff, width, int(experts), _ptr(tile_group), ctypes.c_float(glu[0]),
+                ctypes.c_float(glu[1]), ctypes.c_float(glu[2] if len(glu) > 2 else 1.0), _ptr(self.error_flag), _stream()),
+                "moe experts (gate and up, tiles)")
         else:
             _check(self.lib.ifx_gemm_tcgen05_grouped(_ptr(rows), _ptr(w_up), _ptr(act), cap, ff, width, int(experts), ff,
                                                      _ptr(tile_group), _ptr(None), 2, _ptr(self.error_flag), _stream()),
@@ -1362,6 +1391,119 @@ class CudaKernels:
                                         int(experts), width, _DT[out_dtype], _stream()), "moe_combine")
         self.launches += 5
         return out
+
+    # ------------------------------------------- pairs of mixers, scans with a decayed matrix state
+    def bigram_add(self, x, table, token_ids, state, mul_prev, mul_cur, buckets, vocab, ctx):
+        """x[t] += table[(token before * mul_prev + token * mul_cur) mod buckets], the last row (`buckets`) at position 0;
+        the token before a span's first one is state[slot, 0] (int32), which then takes the span's last token."""
+        T, H = x.shape
+        _need(x.dtype == torch.float32 and x.is_contiguous() and table.is_contiguous() and tuple(table.shape) == (buckets + 1, H)
+              and state is not None and state.dtype == torch.int32, "bigram_add: bad operands")
+        _check(self.lib.ifx_bigram_add(_ptr(x), _ptr(table), _ptr(token_ids), _ptr(ctx.positions), _ptr(ctx.token_req),
+                                       _ptr(ctx.req_slot), _ptr(ctx.cu_seqlens), _ptr(state), ctypes.c_longlong(state.stride(0)),
+                                       T, H, int(vocab), ctypes.c_longlong(mul_prev), ctypes.c_longlong(mul_cur), int(buckets),
+                                       _DT[table.dtype], _stream()), "bigram_add")
+        self.launches += 1
+
+    def rmsnorm_pair(self, x, w_a, eps_a, w_b, eps_b, out_dtype, delta=None):
+        """x += delta (if any); two RMS norms of the same float32 rows, one kernel."""
+        if delta is not None:
+            self.residual_add(x, delta)
+        T, H = x.shape
+        _need(x.dtype == torch.float32 and x.is_contiguous() and w_a.numel() == H and w_b.numel() == H
+              and w_a.dtype == torch.float32 and w_b.dtype == torch.float32, "rmsnorm_pair: bad operands")
+        out_a = torch.empty((T, H), dtype=out_dtype, device=x.device)
+        out_b = torch.empty((T, H), dtype=out_dtype, device=x.device)
+        _check(self.lib.ifx_rmsnorm_pair(_ptr(x), _ptr(w_a), ctypes.c_float(eps_a), _ptr(w_b), ctypes.c_float(eps_b), _ptr(out_a),
+                                         _ptr(out_b), T, H, _DT[out_dtype], _stream()), "rmsnorm_pair")
+        self.launches += 1
+        return out_a, out_b
+
+    def gate_mul(self, a, g, kind):
+        """a * sigmoid(g) (`sigmoid`) or a * silu(g) (`silu`), in a's dtype."""
+        _need(kind in ("sigmoid", "silu") and a.shape == g.shape and a.dtype == g.dtype and a.is_contiguous() and g.is_contiguous(),
+              "gate_mul: bad operands")
+        out = torch.empty_like(a)
+        _check(self.lib.ifx_gate_mul(_ptr(a), _ptr(g), _ptr(out), ctypes.c_longlong(a.numel()), _DT[a.dtype], int(kind == "silu"),
+                                     _stream()), "gate_mul")
+        self.launches += 1
+        return out
+
+    @staticmethod
+    def _rows_f32(t, what):
+        _need(t.dtype == torch.float32 and t.dim() == 2 and t.stride(1) == 1, f"{what}: float32 rows with unit column stride")
+        return ctypes.c_void_p(t.data_ptr()), ctypes.c_longlong(t.stride(0))
+
+    def decay_scan(self, q, k, v, raw, state, ctx, heads, groups, dk, dv, decay, tau=1.0, q_scale=1.0, step_bias=None,
+                   log_rate=None, skip=None):
+        """Per request and head a float32 matrix S, kept in `state` [slots, >= heads dv dk] as [head, value channel, key
+        channel]: S <- diag(w_t) S + k_t v_t^T, o_t = S^T (q_scale q_t) with the new S.  q, k: float32 [T, groups dk]
+        (head h reads group h // (heads / groups)); v: [T, heads dv]; rows may be slices of wider rows.  Returns
+        float32 [T, heads dv].
+        decay `sigmoid_root`: raw [T, heads dk], w = sigmoid(raw)^(1/tau).
+        decay `softplus_step`: raw [T, heads], dt = softplus(raw + step_bias), w = exp(-exp(log_rate) dt) for the whole
+        head, k is multiplied by dt, and skip[h] v_t is added to o_t."""
+        T = q.shape[0]
+        _need(decay in ("sigmoid_root", "softplus_step"), f"decay_scan: unknown decay {decay!r}")
+        mode = 0 if decay == "sigmoid_root" else 1
+        _need(q.shape[1] == groups * dk and k.shape[1] == groups * dk and v.shape[1] == heads * dv
+              and raw.shape[1] == (heads * dk if mode == 0 else heads) and k.shape[0] == T and v.shape[0] == T and raw.shape[0] == T,
+              "decay_scan: the rows do not fit the head counts")
+        _need(state is not None and state.dtype == torch.float32 and state.stride(1) == 1 and state.shape[1] >= heads * dv * dk,
+              "decay_scan: the state does not fit the heads")
+        for vec in (step_bias, log_rate, skip):
+            _need(vec is None or (vec.dtype == torch.float32 and vec.numel() == heads and vec.is_contiguous()),
+                  "decay_scan: per-head vectors are float32 [heads]")
+        out = torch.empty((T, heads * dv), dtype=torch.float32, device=q.device)
+        _check(self.lib.ifx_decay_scan(*self._rows_f32(q, "decay_scan q"), *self._rows_f32(k, "decay_scan k"),
+                                       *self._rows_f32(v, "decay_scan v"), *self._rows_f32(raw, "decay_scan raw"), _ptr(state),
+                                       ctypes.c_longlong(state.stride(0)), _ptr(ctx.req_slot), _ptr(ctx.cu_seqlens), _ptr(out),
+                                       _ptr(step_bias), _ptr(log_rate), _ptr(skip), ctx.num_requests, int(ctx.max_span), int(heads),
+                                       int(groups), int(dk), int(dv), mode, ctypes.c_float(tau), ctypes.c_float(q_scale), 296,
+                                       _stream()), "decay_scan")
+        self.launches += 1
+        return out
+
+    def gated_groupnorm(self, y, gate, w, eps, groups, gate_first, out_dtype):
+        """Rows of y (float32 [T, C]) in `groups` equal parts, each over its own root mean square, times w (of size C, or
+        of a part's size and then the same for every part) and silu(gate) (float32 rows, maybe a slice of wider ones):
+        the gate multiplies before the norm (`gate_first`) or behind it."""
+        T, C = y.shape
+        _need(y.dtype == torch.float32 and y.is_contiguous() and tuple(gate.shape) == (T, C) and w.dtype == torch.float32
+              and w.is_contiguous() and C % groups == 0 and w.numel() in (C, C // groups), "gated_groupnorm: bad operands")
+        out = torch.empty((T, C), dtype=out_dtype, device=y.device)
+        gp, gs = self._rows_f32(gate, "gated_groupnorm gate")
+        _check(self.lib.ifx_gated_groupnorm(_ptr(y), gp, gs, _ptr(w), int(w.numel()), ctypes.c_float(eps), _ptr(out), T, C,
+                                            int(groups), int(bool(gate_first)), _DT[out_dtype], _stream()), "gated_groupnorm")
+        self.launches += 1
+        return out
+
+    def pair_combine(self, a, b, w_a, w_b, c_a, c_b, eps):
+        """float32 [T, C]: c_a a + c_b b, or with weights c_a a / rms(a) * w_a + c_b b / rms(b) * w_b (a, b in any dtype)."""
+        T, C = a.shape
+        _need(a.is_contiguous() and b.is_contiguous() and a.shape == b.shape and (w_a is None) == (w_b is None),
+              "pair_combine: rows of one shape")
+        out = torch.empty((T, C), dtype=torch.float32, device=a.device)
+        _check(self.lib.ifx_pair_combine(_ptr(a), _DT[a.dtype], _ptr(b), _DT[b.dtype], _ptr(w_a), _ptr(w_b), ctypes.c_float(c_a),
+                                         ctypes.c_float(c_b), ctypes.c_float(eps), _ptr(out), T, C, _stream()), "pair_combine")
+        self.launches += 1
+        return out
+
+    def residual_add_vectors(self, x, a, s_a, b=None, s_b=None, b2=None):
+        """x += s_a * a + s_b * (b + b2), element by element along a row (a vector None: ones; b, b2 may be None)."""
+        T, C = x.shape
+        a = self.materialize(a)
+        b = None if b is None else self.materialize(b)
+        b2 = None if b2 is None else self.materialize(b2)
+        if b is not None and b2 is not None and b2.dtype != b.dtype:
+            b2 = b2.to(b.dtype)
+        _need(x.dtype == torch.float32 and x.is_contiguous() and a.shape == x.shape and a.is_contiguous()
+              and (b is None or (b.shape == x.shape and b.is_contiguous())) and (b2 is None or (b is not None and b2.is_contiguous())),
+              "residual_add_vectors: bad operands")
+        _check(self.lib.ifx_residual_add_vectors(_ptr(x), _ptr(a), _DT[a.dtype], _ptr(s_a), _ptr(b), _ptr(b2),
+                                                 _DT[b.dtype] if b is not None else 0, _ptr(s_b), T, C, _stream()),
+               "residual_add_vectors")
+        self.launches += 1
 
     # ---------------------------------------------------------------- sampling
     def argmax(self, logits):

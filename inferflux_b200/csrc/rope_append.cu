@@ -238,7 +238,7 @@ __global__ void norm_rope_append_kernel(const T* __restrict__ qkv, const float* 
                                         const int* __restrict__ req_slot, const int* __restrict__ block_table,
                                         int max_blocks, int page_size, int num_pages, T* __restrict__ kv_pool,
                                         T* __restrict__ q_out, int nq, int nkv_src, int nkv_cache, int d, int d_v,
-                                        int d_row, int write_cache) {
+                                        int d_row, int write_cache, float magnitude, float q_temp_coef, int q_temp_every) {
   __shared__ float scratch[32];
   const int t = blockIdx.x;
   const int head = blockIdx.y;                      // [0, nq) q, [nq, nq + nkv_src) k, then v
@@ -276,6 +276,8 @@ __global__ void norm_rope_append_kernel(const T* __restrict__ qkv, const float* 
     inv_rms = 1.0f / sqrtf(ss / (float)size + norm_eps);
   }
   if (dst == nullptr) return;
+  // queries may grow with the position: 1 + coef ln(floor((pos + 1) / every) + 1)
+  const float q_mult = (is_q && q_temp_every > 0) ? 1.0f + q_temp_coef * logf((float)((pos + 1) / q_temp_every + 1)) : 1.0f;
   const int half_rot = is_v ? 0 : rot / 2;
   for (int j = threadIdx.x; j < (size + 1) / 2; j += blockDim.x) {
     int e0, e1;
@@ -294,11 +296,15 @@ __global__ void norm_rope_append_kernel(const T* __restrict__ qkv, const float* 
     if (j < half_rot) {
       float sn, cs;
       sincosf((float)pos * inv_freq[j], &sn, &cs);
+      sn *= magnitude;
+      cs *= magnitude;
       const float ra = a * cs - c * sn;
       const float rc = c * cs + a * sn;
       a = ra;
       c = rc;
     }
+    a *= q_mult;
+    c *= q_mult;
     if (!is_q) {                      // the cache only ever holds finite values
       a = isfinite(a) ? a : 0.0f;
       c = isfinite(c) ? c : 0.0f;
@@ -353,13 +359,16 @@ extern "C" int ifx_rope_append(const void* qkv, const float* qkv_partial, int nu
 }
 
 // See norm_rope_append_kernel.  nkv_src: key/value heads in the rows of qkv (0: the layer reads another layer's
-// cache and projects queries only); nkv_cache: key/value heads of the cache's pages.
-extern "C" int ifx_norm_rope_append(const void* qkv, const float* qkv_partial, int num_splits, const float* q_norm_w,
-                                    const float* k_norm_w, float norm_eps, const float* inv_freq, int rot,
-                                    int interleaved, const int* positions, const int* token_req, const int* req_slot,
-                                    const int* block_table, int max_blocks, int page_size, int num_pages, void* kv_pool,
-                                    void* q_out, int num_tokens, int nq, int nkv_src, int nkv_cache, int d, int d_v,
-                                    int d_row, int write_cache, int dtype, cudaStream_t stream) {
+// cache and projects queries only); nkv_cache: key/value heads of the cache's pages.  magnitude: what cos and sin are
+// multiplied by; q_temp_every > 0: queries are multiplied by 1 + q_temp_coef ln(floor((pos + 1) / q_temp_every) + 1).
+extern "C" int ifx_norm_rope_append_ex(const void* qkv, const float* qkv_partial, int num_splits, const float* q_norm_w,
+                                       const float* k_norm_w, float norm_eps, const float* inv_freq, int rot,
+                                       int interleaved, const int* positions, const int* token_req, const int* req_slot,
+                                       const int* block_table, int max_blocks, int page_size, int num_pages, void* kv_pool,
+                                       void* q_out, int num_tokens, int nq, int nkv_src, int nkv_cache, int d, int d_v,
+                                       int d_row, int write_cache, float magnitude, float q_temp_coef, int q_temp_every,
+                                       int dtype, cudaStream_t stream) {
+  if (q_temp_every < 0) return IFX_E_BADARG;
   if (num_tokens <= 0) return 0;
   if (nq <= 0 || nkv_src < 0 || d <= 0 || d_v <= 0 || rot < 0 || rot > d || rot % 2) return IFX_E_BADARG;
   if (rot > 0 && inv_freq == nullptr) return IFX_E_BADARG;
@@ -377,14 +386,27 @@ extern "C" int ifx_norm_rope_append(const void* qkv, const float* qkv_partial, i
     norm_rope_append_kernel<float><<<grid, threads, 0, stream>>>(
         (const float*)qkv, qkv_partial, num_splits, split_stride, q_norm_w, k_norm_w, norm_eps, inv_freq, rot,
         interleaved, positions, token_req, req_slot, block_table, max_blocks, page_size, num_pages, (float*)kv_pool,
-        (float*)q_out, nq, nkv_src, nkv_cache, d, d_v, d_row, write_cache);
+        (float*)q_out, nq, nkv_src, nkv_cache, d, d_v, d_row, write_cache, magnitude, q_temp_coef, q_temp_every);
   else if (dtype == IFX_DT_BF16)
     norm_rope_append_kernel<__nv_bfloat16><<<grid, threads, 0, stream>>>(
         (const __nv_bfloat16*)qkv, qkv_partial, num_splits, split_stride, q_norm_w, k_norm_w, norm_eps, inv_freq, rot,
         interleaved, positions, token_req, req_slot, block_table, max_blocks, page_size, num_pages,
-        (__nv_bfloat16*)kv_pool, (__nv_bfloat16*)q_out, nq, nkv_src, nkv_cache, d, d_v, d_row, write_cache);
+        (__nv_bfloat16*)kv_pool, (__nv_bfloat16*)q_out, nq, nkv_src, nkv_cache, d, d_v, d_row, write_cache, magnitude,
+        q_temp_coef, q_temp_every);
   else
     return IFX_E_DTYPE;
   IFX_CHECK_LAUNCH();
   return 0;
+}
+
+extern "C" int ifx_norm_rope_append(const void* qkv, const float* qkv_partial, int num_splits, const float* q_norm_w,
+                                    const float* k_norm_w, float norm_eps, const float* inv_freq, int rot,
+                                    int interleaved, const int* positions, const int* token_req, const int* req_slot,
+                                    const int* block_table, int max_blocks, int page_size, int num_pages, void* kv_pool,
+                                    void* q_out, int num_tokens, int nq, int nkv_src, int nkv_cache, int d, int d_v,
+                                    int d_row, int write_cache, int dtype, cudaStream_t stream) {
+  return ifx_norm_rope_append_ex(qkv, qkv_partial, num_splits, q_norm_w, k_norm_w, norm_eps, inv_freq, rot, interleaved,
+                                 positions, token_req, req_slot, block_table, max_blocks, page_size, num_pages, kv_pool,
+                                 q_out, num_tokens, nq, nkv_src, nkv_cache, d, d_v, d_row, write_cache, 1.0f, 0.0f, 0, dtype,
+                                 stream);
 }
