@@ -658,9 +658,9 @@ class CudaKernels:
         rotation; `dv`: the values' head size if it is not `d` (cache rows hold the larger of the two);
         `own_kv` False: the rows hold queries only and nothing is stored; `q_temp` = (coef, every): the queries are
         multiplied by 1 + coef ln(floor((p + 1) / every) + 1) at position p.  A table whose cos and sin are made longer
-        (`rotary.magnitude`) takes the general kernel too."""
+        (`rotary.magnitude`) or cache rows longer than a head take the general kernel too."""
         if (q_norm is not None or k_norm is not None or (dv is not None and dv != d) or not own_kv or q_temp is not None
-                or (rotary is not None and rotary.magnitude != 1.0)):
+                or (rotary is not None and rotary.magnitude != 1.0) or (cache.kv is not None and cache.kv.shape[-1] != d)):
             return self._norm_rope_append(qkv, bias, rotary, nq, nkv, d, ctx, cache, q_norm, k_norm, norm_eps,
                                           d if dv is None else dv, own_kv, q_temp)
         partial, splits = None, 0
@@ -733,7 +733,8 @@ class CudaKernels:
         `chunk`: a query at position p sees keys from (p // chunk) * chunk on; `sink`: one more unit in the
         softmax's denominator (True), or exp of a learned number per head (a float32 tensor [nq]); `dv`: the values'
         head size if it is not `d`."""
-        if chunk or torch.is_tensor(sink) or sink or (dv is not None and dv != d):
+        if (chunk or torch.is_tensor(sink) or sink or (dv is not None and dv != d)
+                or (cache.kv is not None and cache.kv.shape[-1] != d)):      # cache rows longer than a head
             return self._attention_masked(q, nq, nkv, d, d if dv is None else dv, window, chunk, sink, scale, ctx, cache)
         T = q.shape[0]
         kv, table = cache.kv, cache.block_table

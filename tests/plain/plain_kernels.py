@@ -92,7 +92,7 @@ class PlainKernels:
     def rope_append(self, qkv, bias, rotary, nq, nkv, d, ctx, cache, q_norm=None, k_norm=None, norm_eps=0.0, dv=None,
                     own_kv=True, q_temp=None):
         if (q_norm is not None or k_norm is not None or (dv is not None and dv != d) or not own_kv or q_temp is not None
-                or (rotary is not None and rotary.magnitude != 1.0)):
+                or (rotary is not None and rotary.magnitude != 1.0) or (cache.kv is not None and cache.kv.shape[-1] != d)):
             return self._norm_rope_append(qkv, rotary, nq, nkv, d, d if dv is None else dv, ctx, cache, q_norm, k_norm,
                                           norm_eps, own_kv, q_temp)
         T = qkv.shape[0]
@@ -171,7 +171,7 @@ class PlainKernels:
         dv = d if dv is None else dv
         T = q.shape[0]
         P = cache.page_size
-        if chunk or torch.is_tensor(sink) or sink or dv != d:
+        if chunk or torch.is_tensor(sink) or sink or dv != d or cache.kv.shape[-1] != d:
             out = torch.empty((T, nq, dv), dtype=q.dtype, device=q.device)
             qv = q.view(T, nq, d).to(self.acc)
             pos_all, req_all, slots = ctx.positions.tolist(), ctx.token_req.tolist(), ctx.req_slot.tolist()
