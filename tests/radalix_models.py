@@ -93,7 +93,7 @@ def write_model(raw, out_dir, seed):
     """Random weights for `raw`, then made sharp: the queries' and keys' projections are large so that attention is
     peaked, both embedding tables so that tokens and pairs of tokens differ, norm weights and the layers' output vectors
     are spread, the convolutions' taps are not small, decays spread from slow to fast, step sizes from small to large,
-    sinks from negligible to dominant, and the router decides clearly."""
+    sinks from negligible to dominant, and the router's scores are spread without reaching one."""
     from inferflux_b200.config import config_from_dict
     from inferflux_b200.weights import SafetensorsFile, write_random_model, write_safetensors
     cfg = config_from_dict(raw)
@@ -128,7 +128,7 @@ def write_model(raw, out_dir, seed):
         elif n.endswith(".ls1") or n.endswith(".ls2"):
             tensors[n] = 0.5 + torch.rand(t.shape, generator=g)
         elif n.endswith(".mlp.router"):
-            tensors[n] = t * 10.0
+            tensors[n] = t * 1.5                           # sigmoid scores must stay apart: far-out logits all round to one
         elif ".mlp.e" in n or ".mlp.shared." in n:
             tensors[n] = t * 3.0
     write_safetensors(path, tensors, metadata={"format": "pt"})
