@@ -1056,6 +1056,249 @@ def run_design_benarax(args, pk):
     return 0
 
 
+# ---------------------------------------------------------------- Radalix beside Benarax, the closest existing model
+def radalix_config(shape, layers=0):
+    """Radalix at the sizes of `benarax_config`: layers of a pair of mixers, the two kinds taking turns.  Left: attention
+    with the Qwen2 shape's query heads of 128 over two (1.5B) or four (7B) key/value heads, four taps behind the
+    projections; without positions, with a query multiplier and an output gate in one kind, with 64 turned elements,
+    slowed frequencies, a window of 8,192 and a learned sink in the other.  Right: a matrix state per head with a decay per
+    key channel (heads of 64 keys x 128 values) or a selective state-space recurrence (heads of 64 values, a state of
+    128, one group, four taps).  Every layer a mixture of 16 gated experts of which a token uses 3, plus one that every
+    token uses, sized so that a token's active feed-forward parameters equal the Qwen2 shape's."""
+    from inferflux_b200.config import RadalixConfig
+    s = DESIGN_SHAPES[shape]
+    q = qwen7b_config(s["qwen"])
+    w, inter = s["width"], q.intermediate_size
+    n = layers or q.num_hidden_layers
+    ff = (inter // 4) // 64 * 64
+    moe = {"kind": "moe", "expert": {"ff": ff}, "router": {"experts": 16, "top": 3}, "shared": {"ff": ff}}
+    rot = {"base": 10000.0, "dims": 64, "scaling": {"factor": 40.0, "original": 4096, "fast": 32.0, "slow": 1.0}}
+    left = {"heads": s["heads"], "kv_heads": q.num_key_value_heads, "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "conv": 4}
+    out = []
+    for i in range(n):
+        if i % 2 == 0:
+            out.append({"type": "parallel", "mlp": moe, "mixer": {
+                "left": {**left, "q_temp": {"coef": 0.1, "every": 1024}},
+                "right": {"heads": w // 128, "dim": 64, "vdim": 128, "tau": 16.0}}})
+        else:
+            out.append({"type": "parallel_2", "mlp": moe, "mixer": {
+                "left": {**left, "mask": {"size": 8192}, "rot": rot}, "left_scale": 1.0, "right_scale": 1.0,
+                "right": {"heads": w // 64, "vdim": 64, "state": 128, "groups": 1, "norm_groups": 1, "conv": 4}}})
+    return RadalixConfig.from_dict({"architecture": "Radalix", "vocab": s["vocab"], "width": w, "norm": {"eps": 1e-6},
+                                    "embedding": {"scale": 1.0, "bigram": {"buckets": 65521, "mul_prev": 31, "mul_cur": 17}},
+                                    "logit_softcap": 30.0, "layers": out})
+
+
+def radalix_costs(cfg, batch, context, tokens):
+    """(bytes a decode step must read or write, FLOPs of a prefill of `tokens`): matrices (a token's experts, and at most
+    all of them), recurrent state in and out, cached keys and values."""
+    w, step_bytes, flops = cfg.width, 0, 0
+    for layer in cfg.layers:
+        l, r, mlp = layer["mixer"]["left"], layer["mixer"]["right"], layer["mlp"]
+        qd, kd, vd = l["heads"] * l["dim"], l["kv_heads"] * l["dim"], l["kv_heads"] * l["vdim"]
+        params = w * (qd + kd + vd) + l["heads"] * l["vdim"] * w * (2 if layer["type"] == "parallel" else 1)
+        keys = min(context, l["mask"]["size"]) if l.get("mask") else context
+        step_bytes += batch * keys * (kd + vd) * 2
+        flops += 2 * l["heads"] * (l["dim"] + l["vdim"]) * (tokens * (tokens + 1) // 2)
+        if layer["type"] == "parallel":
+            K, V = r["heads"] * r["dim"], r["heads"] * r["vdim"]
+            params += w * (2 * K + 2 * V) + 16 * (w + K) + V * w
+            state = r["heads"] * r["dim"] * r["vdim"]
+        else:
+            inner, gn = r["heads"] * r["vdim"], r["groups"] * r["state"]
+            params += w * (2 * inner + 2 * gn + r["heads"]) + inner * w
+            state = r["heads"] * r["state"] * r["vdim"]
+        step_bytes += 2 * batch * state * 4
+        flops += 4 * tokens * state
+        step_bytes += 2 * params
+        flops += 2 * tokens * params
+        if mlp:
+            rt = mlp["router"]
+            shared = (mlp.get("shared") or {}).get("ff", 0)
+            step_bytes += 2 * 3 * w * (mlp["expert"]["ff"] * min(rt["experts"], batch * rt["top"]) + shared)
+            flops += 2 * tokens * 3 * w * (mlp["expert"]["ff"] * rt["top"] + shared)
+    return step_bytes + 2 * cfg.vocab * w, flops + 2 * cfg.vocab * w
+
+
+def radalix_kernels(kernels, rcfg, bcfg, pk, batch, context, tokens):
+    """The new design's kernels beside the like kernels of the closest models, each alone at the layer's sizes: the scan with
+    a decayed matrix state (both decays) beside the delta-rule scan, attention with a learned sink beside attention with a
+    plain one, the convolution behind the projections, the gated norm, the pair's sum and the vector-scaled residual sum
+    beside the scaled sum of both sublayers, plain gated experts beside clamped ones."""
+    import torch
+    from inferflux_b200.cache import CacheManager
+    from inferflux_b200.config import ScheduleEntry
+    from inferflux_b200.engine.batch import StepContext, StepEntry
+    from inferflux_b200.parts import KVCacheSpec
+    dev, bf = "cuda:0", torch.bfloat16
+    hbm, tf = pk["hbm_gbs"] * 1e9, pk["bf16_tflops"] * 1e12
+    gla = next(l for l in rcfg.layers if l["type"] == "parallel")["mixer"]["right"]
+    ssm = next(l for l in rcfg.layers if l["type"] == "parallel_2")["mixer"]["right"]
+    left = next(l for l in rcfg.layers if l["type"] == "parallel_2")["mixer"]["left"]
+    moe = next(l["mlp"] for l in rcfg.layers if l["mlp"])
+    dl = next(l for l in bcfg.layers if l["type"] == "general_delta")["mixer"]
+    w = rcfg.width
+    page, out = 16, {}
+
+    def row(name, ms, bytes_=0, flops=0):
+        roof = max(bytes_ / hbm, flops / tf)
+        out[name] = {"us": round(ms * 1000, 1), "roofline_us": round(roof * 1e6, 1), "frac": round(roof / (ms * 1e-3), 3),
+                     "bound": "hbm" if bytes_ / hbm >= flops / tf else "tensor"}
+
+    def ctx_for(cache, spans, providers=()):
+        entries, starts, slots = [], [], []
+        for rid, n in spans:
+            if rid not in cache:
+                cache.add_request(rid)
+            start = cache.length(rid)
+            cache.reserve(rid, start + n)
+            entries.append(StepEntry(rid, [0] * n, []))
+            starts.append(start)
+            slots.append(cache.slot(rid))
+        ctx = StepContext.build(kernels, bf, dev, entries, starts, slots, cache.drain_table_updates(), providers=providers)
+        for g, (idx, pg) in zip(cache.groups, ctx.table_updates):
+            kernels.scatter_i32(g.table, idx, pg)
+        for (rid, n), start in zip(spans, starts):
+            cache.commit(rid, start + n)
+        return ctx
+
+    class _Sections:                                       # asks the kernel table for the attention kernels' work lists
+        def step_sections(self, ctx):
+            return ctx.kernels.attention_sections(ctx)
+
+    nq, nkv, d = left["heads"], left["kv_heads"], left["dim"]
+    for what, spans_a, spans_b in (("decode", [(f"r{i}", context - 1) for i in range(batch)], [(f"r{i}", 1) for i in range(batch)]),
+                                   ("prefill", [], [("p", tokens)])):
+        T = sum(n for _r, n in spans_b)
+        keys = sum((context if what == "decode" else (n * (n + 1)) // 2) for _r, n in spans_b)
+        pages = (batch * context if what == "decode" else tokens) // page + 2 * batch + 2
+        cached = batch * context if what == "decode" else tokens
+        cache = CacheManager([(KVCacheSpec(nkv, d, None), None)], page_size=page, num_pages=pages, max_seqs=batch,
+                             max_seq_len=max(context, tokens) + 16, dtype=bf, device=dev)
+        cache.groups[0].pool.normal_()
+        if spans_a:
+            ctx_for(cache, spans_a)
+        ctx = ctx_for(cache, spans_b, providers=[_Sections()])
+        view = cache.view(ScheduleEntry(0, 0))
+        q = (torch.randn(T, nq * d, device=dev) * 0.3).to(bf)
+        sinks = torch.randn(nq, device=dev)
+        for name, sink in (("attention with a learned sink", sinks), ("attention with a plain sink (the closest model's)", True)):
+            ms = _event_times(lambda: kernels.attention(q, nq, nkv, d, 8192, d ** -0.5, ctx, view, sink=sink))
+            row(f"{name}, {what}", ms, bytes_=cached * nkv * 2 * d * 2 + 2 * T * nq * d * 2, flops=4 * nq * d * keys)
+        # the convolution behind the stacked projections, then rotation, query multiplier and cache rows
+        width = (nq + 2 * nkv) * d
+        qkv = torch.randn(T, width, device=dev).to(bf)
+        taps = torch.randn(width, 4, device=dev)
+        cstate = torch.zeros(batch, 1, 3, width, device=dev)
+        ms = _event_times(lambda: kernels.short_conv(qkv, taps, 4, cstate, 0, ctx, add_input=False))
+        row(f"convolution behind the projections, {T} rows ({what})", ms, bytes_=T * width * 4 + (2 * len(spans_b) * 3 * width * 4 if what == "decode" else 0))
+        del cache
+        # the scans: state in and out, float32 inputs, the output
+        sctx = type("C", (), {})()
+        cu = [0]
+        for _r, n in spans_b:
+            cu.append(cu[-1] + n)
+        sctx.cu_seqlens = torch.tensor(cu, dtype=torch.int32, device=dev)
+        sctx.req_slot = torch.arange(len(spans_b), dtype=torch.int32, device=dev)
+        sctx.num_requests, sctx.num_tokens, sctx.max_span = len(spans_b), T, max(n for _r, n in spans_b)
+        H, dk, dv = gla["heads"], gla["dim"], gla["vdim"]
+        state = torch.zeros(batch, H * dk * dv, device=dev)
+        qq, kk, raw = (torch.randn(T, H * dk, device=dev) * 0.1 for _ in range(3))
+        vv = torch.randn(T, H * dv, device=dev) * 0.1
+        ms = _event_times(lambda: kernels.decay_scan(qq, kk, vv, raw, state, sctx, heads=H, groups=H, dk=dk, dv=dv, decay="sigmoid_root",
+                                                     tau=16.0, q_scale=dk ** -0.5))
+        row(f"scan, decay per key channel, {T} tokens ({what})", ms, bytes_=2 * len(spans_b) * H * dk * dv * 4 + T * H * (3 * dk + 2 * dv) * 4)
+        H2, n2, dv2, G2 = ssm["heads"], ssm["state"], ssm["vdim"], ssm["groups"]
+        state2 = torch.zeros(batch, H2 * n2 * dv2, device=dev)
+        bc = [torch.randn(T, G2 * n2, device=dev) * 0.1 for _ in range(2)]
+        xx, dt = torch.randn(T, H2 * dv2, device=dev) * 0.1, torch.randn(T, H2, device=dev)
+        vec = [torch.zeros(H2, device=dev) for _ in range(3)]
+        ms = _event_times(lambda: kernels.decay_scan(bc[0], bc[1], xx, dt, state2, sctx, heads=H2, groups=G2, dk=n2, dv=dv2,
+                                                     decay="softplus_step", step_bias=vec[0], log_rate=vec[1], skip=vec[2]))
+        row(f"scan, decay per head from a step size, {T} tokens ({what})", ms,
+            bytes_=2 * len(spans_b) * H2 * n2 * dv2 * 4 + T * (2 * G2 * n2 + 2 * H2 * dv2 + H2) * 4)
+        HB, DB = dl["heads"], dl["dim"]
+        state3 = torch.zeros(batch, HB * DB * DB, device=dev)
+        proj = torch.randn(T, 5 * HB * DB, device=dev) * 0.1
+        w_raw = torch.randn(T, HB * DB, device=dev)
+        consts = [torch.zeros(HB * DB, device=dev), torch.zeros(HB * DB, device=dev), torch.ones(HB * DB, device=dev)]
+        ms = _event_times(lambda: kernels.delta_rule_scan(proj, w_raw, *consts, 1e-6, HB, DB, state3, sctx, bf))
+        row(f"delta-rule scan of the closest model, {T} tokens ({what})", ms,
+            bytes_=2 * len(spans_b) * HB * DB * DB * 4 + T * HB * DB * (6 * 4 + 4 * 8 + 2))
+        # rows: the two norms, the gated norms, the pair's sum, the residual sum
+        x = torch.randn(T, w, device=dev)
+        wn = torch.ones(w, device=dev)
+        ms = _event_times(lambda: kernels.rmsnorm_pair(x, wn, 1e-6, wn, 1e-6, bf))
+        row(f"two norms of one row, {T} rows", ms, bytes_=T * w * (4 + 2 + 2))
+        ms = _event_times(lambda: kernels.rmsnorm(x, wn, 1e-6, bf))
+        row(f"one norm of a row (the closest model's), {T} rows", ms, bytes_=T * w * (4 + 2))
+        inner = H2 * dv2
+        y, gate = torch.randn(T, inner, device=dev), torch.randn(T, inner, device=dev)
+        wi = torch.ones(inner, device=dev)
+        ms = _event_times(lambda: kernels.gated_groupnorm(y, gate, wi, 1e-6, 1, True, bf))
+        row(f"gate and norm behind the scan, {T} rows", ms, bytes_=T * inner * (4 + 4 + 2))
+        a, b = torch.randn(T, w, device=dev).to(bf), torch.randn(T, w, device=dev)
+        ms = _event_times(lambda: kernels.pair_combine(a, b, wn, wn, 0.5, 0.5, 1e-6))
+        row(f"the pair's sum with both norms, {T} rows", ms, bytes_=T * w * (2 + 4 + 4))
+        f1, f2 = torch.randn(T, w, device=dev).to(bf), torch.randn(T, w, device=dev).to(bf)
+        ms = _event_times(lambda: kernels.residual_add_vectors(x, b, wn, f1, wn, f2))
+        row(f"residual sum with vectors, {T} rows", ms, bytes_=T * w * (8 + 4 + 2 + 2))
+        ms = _event_times(lambda: kernels.residual_add_scaled(x, f1, f2, 0.5))
+        row(f"scaled sum of both sublayers (the closest model's), {T} rows", ms, bytes_=T * w * (8 + 2 + 2))
+        # the experts: plain gated beside clamped gated (the same kernels)
+        h = torch.randn(T, w, device=dev).to(bf)
+        E, top, ff = moe["router"]["experts"], moe["router"]["top"], moe["expert"]["ff"]
+        up = (torch.randn(E, 2 * ff, w, device=dev) * 0.02).to(bf)
+        down = (torch.randn(E, w, ff, device=dev) * 0.02).to(bf)
+        z = torch.randn(T, E, device=dev)
+        ids, wts = kernels.moe_route(z, None, top, kind="sigmoid_normalized", floor=1e-20)
+        ms = _event_times(lambda: kernels.moe_route(z, None, top, kind="sigmoid_normalized", floor=1e-20))
+        row(f"router, sigmoid scores over their sum, {T} rows", ms, bytes_=T * (E + 2) * 4)
+        for name, glu in (("plain gated experts", (float("inf"), 1.0, 0.0)), ("clamped gated experts (the closest model's)", (7.0, 1.702, 1.0))):
+            ms = _event_times(lambda: kernels.moe_experts(h, up, down, ids, wts, E, bf, glu=glu))
+            row(f"{name}, {T} rows", ms, bytes_=min(E, T * top) * 3 * ff * w * 2, flops=2 * T * top * 3 * ff * w)
+        del up, down
+    kernels.check_errors()
+    return out
+
+
+def run_design_radalix(args, pk):
+    """`--design radalix`: decode and prefill throughput of the design at real layer sizes beside Benarax, the closest
+    model, at equal width, layer count, vocabulary and active feed-forward parameters, and its kernels beside the like
+    kernels, one JSON line."""
+    import torch
+    page, batch, context = 16, args.batch, min(args.context, 4096)
+    steps, warmup = max(1, args.steps), max(3, args.warmup)
+    result = {"metric": "decode and prefill tokens/s of another design beside the closest model at equal size",
+              "design": args.design, "dtype": "bf16", "n_gpus": 1, "data": "synthetic: random weights, uniform random token ids",
+              "batch": batch, "context": context, "prefill_tokens": PREFILL_TOKENS, "peaks": pk["source"], "shapes": {}}
+    kernels_table = None
+    for shape in ([args.shape] if args.shape in DESIGN_SHAPES and args.shape != "7b" else sorted(DESIGN_SHAPES)):
+        entry = {}
+        for name in ("radalix", "benarax"):
+            cfg = radalix_config(shape, args.layers) if name == "radalix" else benarax_config(shape, args.layers)
+            longest = context + 4 * (warmup + 3 * steps) + 16 + batch
+            engine = _engine(cfg, page, batch, longest)
+            r = time_decode(engine, cfg, batch, steps, warmup, repeats=3, context=context, e2e=False)
+            pre_ms = time_prefill(engine, cfg, PREFILL_TOKENS, warmup=2, reps=5)
+            step_bytes, flops = (radalix_costs if name == "radalix" else benarax_costs)(cfg, batch, r["ctx"], PREFILL_TOKENS)
+            entry[name] = {"decode_tok_s": round(batch * 1000.0 / r["dev_ms"], 1), "decode_ms_per_step": round(r["dev_ms"], 3),
+                           "decode_hbm_frac": round(step_bytes / (r["dev_ms"] * 1e-3) / 1e9 / pk["hbm_gbs"], 3),
+                           "launches_per_step": round(r["launches"], 1),
+                           "prefill_tok_s": round(PREFILL_TOKENS * 1000.0 / pre_ms, 1), "prefill_ms": round(pre_ms, 2),
+                           "prefill_tensor_frac": round(flops / (pre_ms * 1e-3) / 1e12 / pk["bf16_tflops"], 3)}
+            if name == "radalix" and kernels_table is None:
+                kernels_table = radalix_kernels(engine.kernels, cfg, benarax_config(shape, args.layers), pk, batch, context,
+                                                PREFILL_TOKENS)
+                entry["kernels"] = kernels_table
+            del engine
+            torch.cuda.empty_cache()
+        result["shapes"][shape] = entry
+    print(json.dumps(result))
+    return 0
+
+
+
 def _engine(cfg, page, slots, longest, pages=None, chunk=2048):
     import torch
     from inferflux_b200 import Engine
@@ -1089,7 +1332,7 @@ def main() -> int:
     ap.add_argument("--no-extras", action="store_true", help="skip the PyTorch baseline and the 1.5B-shape points")
     ap.add_argument("--prefill-only", action="store_true",
                     help="time only the 2,048-token prefill and print a short line (for profiling prefill)")
-    ap.add_argument("--design", default="", choices=["", "dafolorn", "zeluzen", "benarax"],
+    ap.add_argument("--design", default="", choices=["", "dafolorn", "zeluzen", "benarax", "radalix"],
                     help="instead of the headline numbers: this design at real layer sizes beside the Qwen2 shape of equal "
                          "size (decode and prefill tokens/s, and its kernels beside the like kernels); --shape picks one size")
     args = ap.parse_args()
@@ -1101,6 +1344,8 @@ def main() -> int:
         return run_design_zeluzen(args, pk)
     if args.design == "benarax":
         return run_design_benarax(args, pk)
+    if args.design == "radalix":
+        return run_design_radalix(args, pk)
     if args.design:
         return run_design(args, pk)
     if args.gpus != 1:

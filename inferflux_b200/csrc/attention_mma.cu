@@ -269,8 +269,8 @@ attn_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kv_pool
   l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 1);
   l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 2);
   if (window.sink) {                                    // the sink's share, relative to the row's maximum
-    l_lo += exp2f(-m_lo * scale_log2);
-    l_hi += exp2f(-m_hi * scale_log2);
+    l_lo += exp2f(window.sink_log2(h) - m_lo * scale_log2);
+    l_hi += exp2f(window.sink_log2(h) - m_hi * scale_log2);
   }
   const float i_lo = l_lo > 0.0f ? 1.0f / l_lo : 0.0f, i_hi = l_hi > 0.0f ? 1.0f / l_hi : 0.0f;
   const int r_lo = warp * 16 + (lane >> 2), r_hi = r_lo + 8;
@@ -493,7 +493,7 @@ attn_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kv_pool,
     }
     const int head = g * G + row;
     if (num_splits == 1) {
-      if (window.sink && M != -INFINITY) L += exp2f(-M);
+      if (window.sink && M != -INFINITY) L += exp2f(window.sink_log2(g * G + row) - M);
       out[((size_t)t * nq + head) * D + dim] = __float2bfloat16_rn(L > 0.0f ? O / L : 0.0f);
     } else {
       fin_o[row * D + dim] = O;
@@ -535,7 +535,7 @@ attn_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kv_pool,
         L += f * ls[c];
       }
     }
-    if (window.sink && M != -INFINITY) L += exp2f(-M);
+    if (window.sink && M != -INFINITY) L += exp2f(window.sink_log2(g * G + row) - M);
     out[((size_t)t * nq + g * G + row) * D + dim] = __float2bfloat16_rn(L > 0.0f ? O / L : 0.0f);
   }
   cluster.sync();                                       // nobody leaves while its shared memory is being read
@@ -792,7 +792,7 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap pool_map, const bf16*
       }
     }
     if (num_splits == 1) {
-      if (window.sink && M != -INFINITY) L += exp2f(-M);
+      if (window.sink && M != -INFINITY) L += exp2f(window.sink_log2(g * G + row) - M);
     out[((size_t)t * nq + g * G + row) * D + dim] = __float2bfloat16_rn(L > 0.0f ? O / L : 0.0f);
     } else {
       fin_o[row * D + dim] = O;
@@ -832,7 +832,7 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap pool_map, const bf16*
         L += f * ls[c];
       }
     }
-    if (window.sink && M != -INFINITY) L += exp2f(-M);
+    if (window.sink && M != -INFINITY) L += exp2f(window.sink_log2(g * G + row) - M);
     out[((size_t)t * nq + g * G + row) * D + dim] = __float2bfloat16_rn(L > 0.0f ? O / L : 0.0f);
   }
   cluster.sync();
@@ -989,11 +989,13 @@ int ifx_attention_mma_supports(int d) {
 // tiles: int32 [num_tiles, 4] = (request index, first flat row, rows <= 256, first position).
 // max_keys: no request of the step holds more keys than this (sizes the shared-memory copy of the block table).
 // chunk, sink: see KeyMask.
-int ifx_attention_prefill_bf16_ex(const void* q, const void* kv_pool, const int* block_table, const int* tiles,
-                                  const int* req_slot, void* out, int num_tiles, int nq, int nkv, int d, int page_size,
-                                  int max_blocks, int num_pages, int window_size, int chunk, int sink, float scale,
-                                  int max_keys, int* error_flag, cudaStream_t stream) {
-  const KeyMask window{window_size, chunk, sink};
+// sink_values: null, or one learned number per query head (float32 [nq]) that takes the place of the sink's score 0.
+int ifx_attention_prefill_bf16_sink(const void* q, const void* kv_pool, const int* block_table, const int* tiles,
+                                    const int* req_slot, void* out, int num_tiles, int nq, int nkv, int d, int page_size,
+                                    int max_blocks, int num_pages, int window_size, int chunk, int sink,
+                                    const float* sink_values, float scale, int max_keys, int* error_flag,
+                                    cudaStream_t stream) {
+  const KeyMask window{window_size, chunk, sink, sink_values};
   if (num_tiles <= 0) return 0;
   if (nq <= 0 || nkv <= 0 || nq % nkv || page_size <= 0 || max_blocks <= 0 || nq > 65535 || !(scale > 0.0f))
     return IFX_E_BADARG;                                  // the kernels take the maximum before scaling
@@ -1004,6 +1006,15 @@ int ifx_attention_prefill_bf16_ex(const void* q, const void* kv_pool, const int*
                      nkv, page_size, ps, max_blocks, num_pages, window, scale_log2, max_keys, stream)
   IFX_DISPATCH_D(d, CALL)
 #undef CALL
+}
+
+int ifx_attention_prefill_bf16_ex(const void* q, const void* kv_pool, const int* block_table, const int* tiles,
+                                  const int* req_slot, void* out, int num_tiles, int nq, int nkv, int d, int page_size,
+                                  int max_blocks, int num_pages, int window_size, int chunk, int sink, float scale,
+                                  int max_keys, int* error_flag, cudaStream_t stream) {
+  return ifx_attention_prefill_bf16_sink(q, kv_pool, block_table, tiles, req_slot, out, num_tiles, nq, nkv, d, page_size,
+                                         max_blocks, num_pages, window_size, chunk, sink, nullptr, scale, max_keys, error_flag,
+                                         stream);
 }
 
 int ifx_attention_prefill_bf16(const void* q, const void* kv_pool, const int* block_table, const int* tiles,
@@ -1025,11 +1036,11 @@ int ifx_attention_decode_max_splits(int d, int page_size) {
 // num_splits: 1, 2, 4 or 8 blocks (one cluster) share a token's key range; it must divide d.  16 where
 // ifx_attention_decode_max_splits says so (the TMA variant, a cluster size beyond the portable 8).
 // max_keys: no token of the step sees more keys than this.
-int ifx_attention_decode_bf16_ex(const void* q, const void* kv_pool, const int* block_table, const int* decode_meta,
-                                 void* out, int num_items, int nq, int nkv, int d, int page_size, int max_blocks,
-                                 int num_pages, int window_size, int chunk, int sink, float scale, int num_splits,
-                                 int max_keys, int* error_flag, cudaStream_t stream) {
-  const KeyMask window{window_size, chunk, sink};
+int ifx_attention_decode_bf16_sink(const void* q, const void* kv_pool, const int* block_table, const int* decode_meta,
+                                   void* out, int num_items, int nq, int nkv, int d, int page_size, int max_blocks,
+                                   int num_pages, int window_size, int chunk, int sink, const float* sink_values, float scale,
+                                   int num_splits, int max_keys, int* error_flag, cudaStream_t stream) {
+  const KeyMask window{window_size, chunk, sink, sink_values};
   if (num_items <= 0) return 0;
   if (nq <= 0 || nkv <= 0 || nq % nkv || nq / nkv > 16 || page_size <= 0 || max_blocks <= 0 || nkv > 65535 ||
       nq > 65535)
@@ -1060,6 +1071,15 @@ int ifx_attention_decode_bf16_ex(const void* q, const void* kv_pool, const int* 
                     max_keys, stream)
   IFX_DISPATCH_D(d, CALL)
 #undef CALL
+}
+
+int ifx_attention_decode_bf16_ex(const void* q, const void* kv_pool, const int* block_table, const int* decode_meta,
+                                 void* out, int num_items, int nq, int nkv, int d, int page_size, int max_blocks,
+                                 int num_pages, int window_size, int chunk, int sink, float scale, int num_splits,
+                                 int max_keys, int* error_flag, cudaStream_t stream) {
+  return ifx_attention_decode_bf16_sink(q, kv_pool, block_table, decode_meta, out, num_items, nq, nkv, d, page_size,
+                                        max_blocks, num_pages, window_size, chunk, sink, nullptr, scale, num_splits, max_keys,
+                                        error_flag, stream);
 }
 
 int ifx_attention_decode_bf16(const void* q, const void* kv_pool, const int* block_table, const int* decode_meta,

@@ -383,7 +383,7 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __g
     if (!ok && lane == 0) atomicExch(error_flag, 9);
     if (ok && i > 0) {
       tc_fence_after();
-      if (window.sink && m_ref > -INFINITY) l_run += exp2f(-m_ref * scale_log2);     // the sink's share
+      if (window.sink && m_ref > -INFINITY) l_run += exp2f(window.sink_log2(h) - m_ref * scale_log2);     // the sink's share
       const float inv = l_run > 0.0f ? 1.0f / l_run : 0.0f;
       bf16* dst = out + ((size_t)(row0 + q * kBM + row) * nq + h) * D;
 #pragma unroll 1
@@ -449,11 +449,12 @@ int ifx_attention_prefill_tcgen05_supports(int d, int page_size) {
 // q [num_tokens, nq * d] bfloat16, 16-byte aligned.  tiles: int32 [num_tiles, 4] = (request index, first
 // flat row, rows <= 256, first position).
 // chunk, sink: see KeyMask (common.cuh).
-int ifx_attention_prefill_tcgen05_ex(const void* q, int num_tokens, const void* kv_pool, const int* block_table,
-                                     const int* tiles, const int* req_slot, void* out, int num_tiles, int nq, int nkv,
-                                     int d, int page_size, int max_blocks, int num_pages, int window_size, int chunk,
-                                     int sink, float scale, int* error_flag, cudaStream_t stream) {
-  const KeyMask window{window_size, chunk, sink};
+// sink_values: null, or one learned number per query head (float32 [nq]) that takes the place of the sink's score 0.
+int ifx_attention_prefill_tcgen05_sink(const void* q, int num_tokens, const void* kv_pool, const int* block_table,
+                                       const int* tiles, const int* req_slot, void* out, int num_tiles, int nq, int nkv,
+                                       int d, int page_size, int max_blocks, int num_pages, int window_size, int chunk,
+                                       int sink, const float* sink_values, float scale, int* error_flag, cudaStream_t stream) {
+  const KeyMask window{window_size, chunk, sink, sink_values};
   if (num_tiles <= 0) return 0;
   if (!ifx_attention_prefill_tcgen05_supports(d, page_size) || nq <= 0 || nkv <= 0 || nq % nkv || max_blocks <= 0 ||
       num_tiles > 65535 || !(scale > 0.0f) || error_flag == nullptr)
@@ -468,6 +469,15 @@ int ifx_attention_prefill_tcgen05_ex(const void* q, int num_tokens, const void* 
   return launch_prefill_tcgen05<128>((const bf16*)q, num_tokens, (const bf16*)kv_pool, block_table, tiles, req_slot,
                                      (bf16*)out, num_tiles, nq, nkv, page_size, ps, max_blocks, num_pages, window,
                                      scale_log2, error_flag, stream);
+}
+
+int ifx_attention_prefill_tcgen05_ex(const void* q, int num_tokens, const void* kv_pool, const int* block_table,
+                                     const int* tiles, const int* req_slot, void* out, int num_tiles, int nq, int nkv,
+                                     int d, int page_size, int max_blocks, int num_pages, int window_size, int chunk,
+                                     int sink, float scale, int* error_flag, cudaStream_t stream) {
+  return ifx_attention_prefill_tcgen05_sink(q, num_tokens, kv_pool, block_table, tiles, req_slot, out, num_tiles, nq, nkv, d,
+                                            page_size, max_blocks, num_pages, window_size, chunk, sink, nullptr, scale, error_flag,
+                                            stream);
 }
 
 int ifx_attention_prefill_tcgen05(const void* q, int num_tokens, const void* kv_pool, const int* block_table,

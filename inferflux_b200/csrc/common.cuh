@@ -80,9 +80,14 @@ inline int launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t sm
 
 // Which keys a query sees besides "not later than itself": the last `window` of them (> 0), only those of its own
 // stretch of `chunk` positions (> 0), or both; `sink`: the softmax's denominator holds one more unit, a key of score 0
-// that brings no value.
+// that brings no value; with `sink_values` (one learned number per query head) the unit is exp(that number) instead.
 struct KeyMask {
   int window, chunk, sink;
+  const float* sink_values;
+  // the sink's score in units of log2, for kernels that keep maxima and sums as powers of two
+  __device__ __forceinline__ float sink_log2(int head) const {
+    return sink_values ? sink_values[head] * 1.4426950408889634f : 0.0f;
+  }
   __device__ __forceinline__ int first(int pos) const {          // the first key the query at `pos` sees
     int f = window > 0 ? max(0, pos - window + 1) : 0;
     if (chunk > 0) f = max(f, pos / chunk * chunk);

@@ -162,7 +162,8 @@ class CudaKernels:
                    "ifx_moe_experts_ex", "ifx_gemm_tcgen05_grouped_glu", "ifx_latent_attention_mma_rot", "ifx_latent_attention_mma_supports_rot",
                    "ifx_moe_route_kind", "ifx_moe_experts_glu", "ifx_gemm_tcgen05_grouped_glu_offset", "ifx_norm_rope_append_ex",
                    "ifx_attention_generic_sink", "ifx_short_conv_ex", "ifx_decay_scan", "ifx_decay_scan_split", "ifx_bigram_add",
-                   "ifx_rmsnorm_pair", "ifx_gate_mul", "ifx_gated_groupnorm", "ifx_pair_combine", "ifx_residual_add_vectors"):
+                   "ifx_rmsnorm_pair", "ifx_gate_mul", "ifx_gated_groupnorm", "ifx_pair_combine", "ifx_residual_add_vectors",
+                   "ifx_attention_prefill_tcgen05_sink", "ifx_attention_prefill_bf16_sink", "ifx_attention_decode_bf16_sink"):
             getattr(self.lib, fn).restype = ctypes.c_int
         self.lib.ifx_delta_rule_scratch_floats.restype = ctypes.c_longlong
         self.lib.ifx_sample_scratch_bytes.restype = ctypes.c_longlong
@@ -812,7 +813,7 @@ class CudaKernels:
         if sink_values is not None:
             _need(sink_values.dtype == torch.float32 and sink_values.numel() == nq and sink_values.is_contiguous(),
                   "attention: the learned sink is float32 [heads]")
-        if (sink_values is None and q.dtype == torch.bfloat16 and d == dv == d_row and nq // nkv <= 16 and self.lib.ifx_attention_mma_supports(d)
+        if (q.dtype == torch.bfloat16 and d == dv == d_row and nq // nkv <= 16 and self.lib.ifx_attention_mma_supports(d)
                 and os.environ.get("INFERFLUX_B200_MASKED_TILES", "1") != "0"):
             # the tiled kernels: prompt portions on mma.sync tiles, single tokens on the cluster kernel
             if "attn.prefill_tiles" not in ctx.extra:          # a step context built without the mixer as a provider
@@ -820,15 +821,16 @@ class CudaKernels:
                     ctx.extra[name] = torch.tensor(vals, dtype=torch.int32, device=q.device)
                     ctx.extra_len[name] = len(vals)
             num_tiles = ctx.extra_len["attn.prefill_tiles"] // 4
-            common = (cache.page_size, table.shape[1], kv.shape[0], win, int(chunk or 0), int(bool(sink)), ctypes.c_float(scale))
+            common = (cache.page_size, table.shape[1], kv.shape[0], win, int(chunk or 0),
+                      int(sink_values is not None or bool(sink)), _ptr(sink_values), ctypes.c_float(scale))
             if num_tiles and self.tensor_core_prefill and self.lib.ifx_attention_prefill_tcgen05_supports(d, cache.page_size):
-                _check(self.lib.ifx_attention_prefill_tcgen05_ex(
+                _check(self.lib.ifx_attention_prefill_tcgen05_sink(
                     _ptr(q), T, _ptr(kv), _ptr(table), _ptr(ctx.extra["attn.prefill_tiles"]), _ptr(ctx.req_slot), _ptr(out),
                     num_tiles, nq, nkv, d, *common, _ptr(self.error_flag), _stream()),
                     "attention (masked, prompt portions, tcgen05)")
                 self.launches += 1
             elif num_tiles:
-                _check(self.lib.ifx_attention_prefill_bf16_ex(
+                _check(self.lib.ifx_attention_prefill_bf16_sink(
                     _ptr(q), _ptr(kv), _ptr(table), _ptr(ctx.extra["attn.prefill_tiles"]), _ptr(ctx.req_slot), _ptr(out),
                     num_tiles, nq, nkv, d, *common, int(ctx.max_kv_len), _ptr(self.error_flag), _stream()),
                     "attention (masked, prompt portions)")
@@ -841,7 +843,7 @@ class CudaKernels:
                 if chunk:
                     max_keys = min(max_keys, int(chunk))
                 splits = self.decode_splits(n, nkv, max_keys, int(self.lib.ifx_attention_decode_max_splits(d, cache.page_size)))
-                _check(self.lib.ifx_attention_decode_bf16_ex(
+                _check(self.lib.ifx_attention_decode_bf16_sink(
                     _ptr(q), _ptr(kv), _ptr(table), _ptr(ctx.extra["attn.decode_meta"]), _ptr(out), n, nq, nkv, d, *common,
                     splits, max_keys, _ptr(self.error_flag), _stream()), "attention (masked, decoded tokens)")
                 self.launches += 1
@@ -1456,13 +1458,16 @@ class CudaKernels:
             _need(vec is None or (vec.dtype == torch.float32 and vec.numel() == heads and vec.is_contiguous()),
                   "decay_scan: per-head vectors are float32 [heads]")
         out = torch.empty((T, heads * dv), dtype=torch.float32, device=q.device)
+        scratch = None                                     # steps with long spans make their decays in a pass of their own
+        if ctx.max_span >= 64:
+            scratch = torch.empty(T * (heads * dk if mode == 0 else 2 * heads), dtype=torch.float32, device=q.device)
         _check(self.lib.ifx_decay_scan(*self._rows_f32(q, "decay_scan q"), *self._rows_f32(k, "decay_scan k"),
                                        *self._rows_f32(v, "decay_scan v"), *self._rows_f32(raw, "decay_scan raw"), _ptr(state),
                                        ctypes.c_longlong(state.stride(0)), _ptr(ctx.req_slot), _ptr(ctx.cu_seqlens), _ptr(out),
-                                       _ptr(step_bias), _ptr(log_rate), _ptr(skip), ctx.num_requests, int(ctx.max_span), int(heads),
+                                       _ptr(step_bias), _ptr(log_rate), _ptr(skip), ctx.num_requests, T, int(ctx.max_span), int(heads),
                                        int(groups), int(dk), int(dv), mode, ctypes.c_float(tau), ctypes.c_float(q_scale), 296,
-                                       _stream()), "decay_scan")
-        self.launches += 1
+                                       _ptr(scratch), _stream()), "decay_scan")
+        self.launches += 1 + int(scratch is not None)
         return out
 
     def gated_groupnorm(self, y, gate, w, eps, groups, gate_first, out_dtype):

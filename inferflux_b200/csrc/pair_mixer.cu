@@ -116,6 +116,42 @@ __global__ void __launch_bounds__(256) gated_groupnorm_kernel(const float* __res
   }
 }
 
+// The same for few, long parts: the whole block works on one part after the other.
+__global__ void __launch_bounds__(512) gated_groupnorm_wide_kernel(const float* __restrict__ y, const float* __restrict__ gate,
+                                                                   long long gate_stride, const float* __restrict__ w,
+                                                                   int w_size, float eps, void* __restrict__ out, int C,
+                                                                   int groups, int gate_first, int out_dtype) {
+  __shared__ float scratch[32];
+  const int t = blockIdx.x;
+  const int part = C / groups;
+  const float* yr = y + (size_t)t * C;
+  const float* gr = gate + (size_t)t * gate_stride;
+  for (int p = 0; p < groups; ++p) {
+    float ss = 0.0f;
+    for (int e = threadIdx.x; e < part; e += blockDim.x) {
+      const int c = p * part + e;
+      float v = yr[c];
+      if (gate_first) {
+        const float gv = gr[c];
+        v *= gv / (1.0f + expf(-gv));
+      }
+      ss = fmaf(v, v, ss);
+    }
+    ss = block_sum(ss, scratch);
+    const float inv = rsqrtf(ss / (float)part + eps);
+    for (int e = threadIdx.x; e < part; e += blockDim.x) {
+      const int c = p * part + e;
+      const float gv = gr[c];
+      const float sg = gv / (1.0f + expf(-gv));
+      float v = yr[c];
+      if (gate_first) v *= sg;
+      v = v * inv * w[w_size == C ? c : e];
+      if (!gate_first) v *= sg;
+      store_from_f32(out, out_dtype, (size_t)t * C + c, v);
+    }
+  }
+}
+
 __global__ void pair_combine_kernel(const void* __restrict__ a, int a_dtype, const void* __restrict__ b, int b_dtype,
                                     const float* __restrict__ w_a, const float* __restrict__ w_b, float c_a, float c_b,
                                     float eps, float* __restrict__ out, int C) {
@@ -211,9 +247,16 @@ int ifx_gated_groupnorm(const float* y, const float* gate, long long gate_stride
   if (T <= 0) return 0;
   if (C <= 0 || groups <= 0 || C % groups || (w_size != C && w_size != C / groups) || gate_stride < C) return IFX_E_BADARG;
   if (out_dtype != IFX_DT_F32 && out_dtype != IFX_DT_BF16) return IFX_E_DTYPE;
-  const int warps = groups >= 8 ? 8 : groups;
-  gated_groupnorm_kernel<<<T, warps * 32, 0, stream>>>(y, gate, gate_stride, w, w_size, eps, out, C, groups, gate_first,
-                                                      out_dtype);
+  const int part = C / groups;
+  if (groups < 8 && part > 64) {                            // few long parts: a block per row takes them in turn
+    const int threads = part >= 2048 ? 512 : (part >= 256 ? 256 : ((part + 31) / 32) * 32);
+    gated_groupnorm_wide_kernel<<<T, threads, 0, stream>>>(y, gate, gate_stride, w, w_size, eps, out, C, groups, gate_first,
+                                                           out_dtype);
+  } else {
+    const int warps = groups >= 8 ? 8 : groups;
+    gated_groupnorm_kernel<<<T, warps * 32, 0, stream>>>(y, gate, gate_stride, w, w_size, eps, out, C, groups, gate_first,
+                                                        out_dtype);
+  }
   IFX_CHECK_LAUNCH();
   return 0;
 }
