@@ -1408,17 +1408,29 @@ class CudaKernels:
                                        _DT[table.dtype], _stream()), "bigram_add")
         self.launches += 1
 
-    def rmsnorm_pair(self, x, w_a, eps_a, w_b, eps_b, out_dtype, delta=None):
-        """x += delta (if any); two RMS norms of the same float32 rows, one kernel."""
+    def rmsnorm_pair(self, x, w_a, eps_a, w_b, eps_b, out_dtype, delta=None, vectors=None):
+        """x += delta (if any); two RMS norms of the same float32 rows, one kernel.  `vectors` (a.s_a, b, s_b, b2 as in
+        residual_add_vectors): x += s_a * a + s_b * (b + b2) in the same kernel."""
         if delta is not None:
             self.residual_add(x, delta)
         T, H = x.shape
+        va = vb = vb2 = vsa = vsb = None
+        if vectors is not None:
+            va, vsa, vsb = self.materialize(vectors.a), vectors.s_a, vectors.s_b
+            vb = None if vectors.b is None else self.materialize(vectors.b)
+            vb2 = None if vectors.b2 is None else self.materialize(vectors.b2)
+            if vb is not None and vb2 is not None and vb2.dtype != vb.dtype:
+                vb2 = vb2.to(vb.dtype)
+            _need(va.shape == x.shape and va.is_contiguous() and (vb is None or (vb.shape == x.shape and vb.is_contiguous()))
+                  and (vb2 is None or (vb is not None and vb2.is_contiguous())), "rmsnorm_pair: the sum's rows do not fit")
         _need(x.dtype == torch.float32 and x.is_contiguous() and w_a.numel() == H and w_b.numel() == H
               and w_a.dtype == torch.float32 and w_b.dtype == torch.float32, "rmsnorm_pair: bad operands")
         out_a = torch.empty((T, H), dtype=out_dtype, device=x.device)
         out_b = torch.empty((T, H), dtype=out_dtype, device=x.device)
         _check(self.lib.ifx_rmsnorm_pair(_ptr(x), _ptr(w_a), ctypes.c_float(eps_a), _ptr(w_b), ctypes.c_float(eps_b), _ptr(out_a),
-                                         _ptr(out_b), T, H, _DT[out_dtype], _stream()), "rmsnorm_pair")
+                                         _ptr(out_b), T, H, _DT[out_dtype], _ptr(va), _DT[va.dtype] if va is not None else 0,
+                                         _ptr(vsa), _ptr(vb), _ptr(vb2), _DT[vb.dtype] if vb is not None else 0, _ptr(vsb),
+                                         _stream()), "rmsnorm_pair")
         self.launches += 1
         return out_a, out_b
 

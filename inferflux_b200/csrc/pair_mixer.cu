@@ -53,14 +53,27 @@ __global__ void bigram_add_kernel(float* __restrict__ x, const T* __restrict__ t
     x[(size_t)t * hidden + c] += to_f32(table[(size_t)row * hidden + c]);
 }
 
-__global__ void rmsnorm_pair_kernel(const float* __restrict__ x, const float* __restrict__ w_a, float eps_a,
+// With `a`: the row first takes x += s_a * a + s_b * (b + b2) (the sum residual_add_vectors makes), in the same pass.
+__global__ void rmsnorm_pair_kernel(float* __restrict__ x, const float* __restrict__ w_a, float eps_a,
                                     const float* __restrict__ w_b, float eps_b, void* __restrict__ out_a,
-                                    void* __restrict__ out_b, int hidden, int out_dtype) {
+                                    void* __restrict__ out_b, int hidden, int out_dtype, const void* __restrict__ a,
+                                    int a_dtype, const float* __restrict__ s_a, const void* __restrict__ b,
+                                    const void* __restrict__ b2, int b_dtype, const float* __restrict__ s_b) {
   __shared__ float scratch[32];
   const size_t base = (size_t)blockIdx.x * hidden;
   float ss = 0.0f;
   for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
-    const float v = x[base + c];
+    float v = x[base + c];
+    if (a != nullptr) {
+      float sum = load_as_f32(a, a_dtype, base + c) * (s_a ? s_a[c] : 1.0f);
+      if (b != nullptr) {
+        float f = load_as_f32(b, b_dtype, base + c);
+        if (b2 != nullptr) f += load_as_f32(b2, b_dtype, base + c);
+        sum = fmaf(f, s_b ? s_b[c] : 1.0f, sum);
+      }
+      v += sum;
+      x[base + c] = v;                                     // read again below by the thread that wrote it
+    }
     ss = fmaf(v, v, ss);
   }
   ss = block_sum(ss, scratch);
@@ -222,13 +235,17 @@ int ifx_bigram_add(float* x, const void* table, const int* tokens, const int* po
   return 0;
 }
 
-int ifx_rmsnorm_pair(const float* x, const float* w_a, float eps_a, const float* w_b, float eps_b, void* out_a, void* out_b,
-                     int T, int hidden, int out_dtype, cudaStream_t stream) {
+int ifx_rmsnorm_pair(float* x, const float* w_a, float eps_a, const float* w_b, float eps_b, void* out_a, void* out_b,
+                     int T, int hidden, int out_dtype, const void* a, int a_dtype, const float* s_a, const void* b,
+                     const void* b2, int b_dtype, const float* s_b, cudaStream_t stream) {
   if (T <= 0) return 0;
-  if (hidden <= 0) return IFX_E_BADARG;
+  if (hidden <= 0 || (a == nullptr && b != nullptr) || (b == nullptr && b2 != nullptr)) return IFX_E_BADARG;
   if (out_dtype != IFX_DT_F32 && out_dtype != IFX_DT_BF16) return IFX_E_DTYPE;
+  for (int dt : {a_dtype, b_dtype})
+    if (dt != IFX_DT_F32 && dt != IFX_DT_BF16) return IFX_E_DTYPE;
   const int threads = hidden >= 1024 ? 512 : (hidden >= 256 ? 256 : ((hidden + 31) / 32) * 32);
-  rmsnorm_pair_kernel<<<T, threads, 0, stream>>>(x, w_a, eps_a, w_b, eps_b, out_a, out_b, hidden, out_dtype);
+  rmsnorm_pair_kernel<<<T, threads, 0, stream>>>(x, w_a, eps_a, w_b, eps_b, out_a, out_b, hidden, out_dtype, a, a_dtype, s_a, b,
+                                                 b2, b_dtype, s_b);
   IFX_CHECK_LAUNCH();
   return 0;
 }

@@ -67,11 +67,23 @@ class NormedDelta:
         ctx.kernels.postnorm_add(x, self.y, self.weight, self.eps)
 
 
+class VectorScaledDelta:
+    """Two sublayers' outputs that join the residual stream together, each times a learned vector along the row:
+    x += s_a * a + s_b * (b + b2) (a vector None: ones; b, b2 may be None).  A block hands it on as `pending`, so that
+    a block whose norm kernel takes it (`ctx.kernels.rmsnorm_pair(..., vectors=...)`) adds and norms in one pass."""
+
+    def __init__(self, a, s_a, b=None, s_b=None, b2=None):
+        self.a, self.s_a, self.b, self.s_b, self.b2 = a, s_a, b, s_b, b2
+
+    def add_to(self, x: torch.Tensor, ctx) -> None:
+        ctx.kernels.residual_add_vectors(x, self.a, self.s_a, self.b, self.s_b, self.b2)
+
+
 def settle_pending(x: torch.Tensor, pending, ctx) -> None:
     """x += pending, whatever kind of delta it is."""
     if pending is None:
         return
-    if isinstance(pending, NormedDelta):
+    if isinstance(pending, (NormedDelta, VectorScaledDelta)):
         pending.add_to(x, ctx)
     else:
         ctx.kernels.residual_add(x, pending)

@@ -10,7 +10,7 @@ from typing import Optional
 import torch
 
 from ..weights.loader import TensorSpec
-from .base import Block, NormedDelta, StateSpec, StreamMerge, register_part, settle_pending
+from .base import Block, NormedDelta, StateSpec, StreamMerge, VectorScaledDelta, register_part, settle_pending
 from .norm import RMSNorm
 
 
@@ -245,7 +245,8 @@ class ParallelNormsBlock(Block):
 
     params: ffn (False: the layer has a mixer only), hidden_size, layer_scale (None: no vectors; or tensor names
     {mixer, ffn}).  Parts: norm_mixer, mixer and, with a feed-forward, norm_ffn, ffn.  A feed-forward may hand back two
-    outputs (a pair: a mixture's and a shared expert's); the sum takes both."""
+    outputs (a pair: a mixture's and a shared expert's); the sum takes both.  The sum travels unadded (`pending`), so that
+    the next layer of this kind adds it in the kernel that makes its two norms."""
 
     def __init__(self, spec, parts):
         self.has_ffn = bool(spec.params.get("ffn", True))
@@ -276,20 +277,23 @@ class ParallelNormsBlock(Block):
     def forward(self, x, pending, ctx, cache):
         k = ctx.kernels
         if self.has_ffn:
-            h_m, h_f = k.rmsnorm_pair(x, self.norm_mixer.weight, self.norm_mixer.eps, self.norm_ffn.weight, self.norm_ffn.eps,
-                                      ctx.dtype, delta=_settled(x, pending, ctx))
+            if isinstance(pending, VectorScaledDelta):
+                h_m, h_f = k.rmsnorm_pair(x, self.norm_mixer.weight, self.norm_mixer.eps, self.norm_ffn.weight,
+                                          self.norm_ffn.eps, ctx.dtype, vectors=pending)
+            else:
+                h_m, h_f = k.rmsnorm_pair(x, self.norm_mixer.weight, self.norm_mixer.eps, self.norm_ffn.weight,
+                                          self.norm_ffn.eps, ctx.dtype, delta=_settled(x, pending, ctx))
         else:
             h_m, h_f = self.norm_mixer.forward(x, _settled(x, pending, ctx), ctx), None
         y = self.mixer.forward(h_m, ctx, cache)
         f = self.ffn.forward(h_f, ctx) if self.has_ffn else None
         f, f2 = f if isinstance(f, tuple) else (f, None)
-        k.residual_add_vectors(x, y, self.s_mixer, f, self.s_ffn, f2)
-        return x, None
+        return x, VectorScaledDelta(y, self.s_mixer, f, self.s_ffn, f2)
 
 
 def _settled(x, pending, ctx):
-    """What is left to add inside the next norm kernel: a plain delta is; one with a norm of its own is added here."""
-    if isinstance(pending, NormedDelta):
+    """What is left to add inside the next norm kernel: a plain delta is; one with a norm or vectors of its own is added here."""
+    if isinstance(pending, (NormedDelta, VectorScaledDelta)):
         pending.add_to(x, ctx)
         return None
     return pending

@@ -336,8 +336,10 @@ class PlainKernels:
         rows = torch.where(pos == 0, torch.full_like(ids, buckets), (before * mul_prev + ids * mul_cur) % buckets)
         x += table[rows].to(torch.float32)
 
-    def rmsnorm_pair(self, x, w_a, eps_a, w_b, eps_b, out_dtype, delta=None):
-        """x += delta (if any); two RMS norms of the same rows."""
+    def rmsnorm_pair(self, x, w_a, eps_a, w_b, eps_b, out_dtype, delta=None, vectors=None):
+        """x += delta (if any; `vectors`: s_a * a + s_b * (b + b2), see residual_add_vectors); two RMS norms of the same rows."""
+        if vectors is not None:
+            self.residual_add_vectors(x, vectors.a, vectors.s_a, vectors.b, vectors.s_b, vectors.b2)
         if delta is not None:
             x += delta.to(torch.float32)
         return self.rmsnorm(x, w_a, eps_a, out_dtype), self.rmsnorm(x, w_b, eps_b, out_dtype)

@@ -171,11 +171,20 @@ def test_two_norms_pair_sum_and_vector_sum(cuda_kernels, dtype, tol, C):
                                         0.5, 1.7, 1e-6)
         assert got.dtype == torch.float32 and float((got.double().cpu() - want.double()).abs().max()) <= 3e-6 * float(want.abs().max())
     f, f2 = torch.randn(T, C, generator=g).to(dtype), torch.randn(T, C, generator=g).to(dtype)
+    from inferflux_b200.parts import VectorScaledDelta
     for args in ((b, wa, f, wb, f2), (b, wa, f, wb, None), (b, wa, None, None, None), (b, None, f, None, f2)):
         xp, xg = x.double().clone(), x.clone().to(DEV)
         plain.residual_add_vectors(xp, *[None if t is None else t.double() for t in args])
         cuda_kernels.residual_add_vectors(xg, *[None if t is None else t.to(DEV) for t in args])
         assert float((xg.double().cpu() - xp).abs().max()) <= 3e-6 * float(xp.abs().max())
+        # the same sum inside the kernel of the two norms
+        xq = x.clone().to(DEV)
+        got = cuda_kernels.rmsnorm_pair(xq, wa.to(DEV), 1e-6, wb.to(DEV), 1e-3, dtype,
+                                        vectors=VectorScaledDelta(*[None if t is None else t.to(DEV) for t in args]))
+        want = plain.rmsnorm_pair(xp.clone(), wa, 1e-6, wb, 1e-3, F64)
+        assert float((xq.double().cpu() - xp).abs().max()) <= 3e-6 * float(xp.abs().max())
+        for u, v_ in zip(got, want):
+            assert float((u.double().cpu() - v_).abs().max()) <= tol * float(v_.abs().max())
 
 
 @pytest.mark.parametrize("dtype,tol", [(torch.float32, 3e-6), (torch.bfloat16, 1e-2)])
