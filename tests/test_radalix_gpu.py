@@ -59,7 +59,7 @@ def _steps(lens_per_step, slot_of):
 # ------------------------------------------------------------------ the scan with a decayed matrix state
 
 @pytest.mark.parametrize("mode", ["sigmoid_root", "softplus_step"])
-@pytest.mark.parametrize("H,G,dk,dv", [(3, 3, 8, 16), (4, 2, 12, 8), (2, 1, 48, 32), (6, 6, 16, 16), (1, 1, 6, 10), (5, 1, 5, 6),
+@pytest.mark.parametrize("H,G,dk,dv", [(3, 3, 8, 16), (4, 2, 12, 8), (2, 1, 56, 24), (6, 6, 16, 16), (1, 1, 6, 10), (5, 1, 5, 6),
                                        (2, 2, 128, 64), (4, 4, 64, 128), (2, 1, 200, 24), (3, 3, 32, 1), (8, 2, 24, 40)])
 def test_decay_scan_over_steps_and_requests(cuda_kernels, mode, H, G, dk, dv):
     """Three requests over four steps: portions of 1 to 37 tokens (more and fewer than the kernel stages at once), a request
@@ -212,7 +212,7 @@ def test_bigram_rows_and_the_token_before_a_step(cuda_kernels, dtype):
     """Three requests over four steps; the token before a step's first one comes from the request's slot, position 0 takes the
     table's last row, hashes beyond 32 bits are taken in 64."""
     plain = PlainKernels(wide=True)
-    vocab, H, buckets, mp, mc = 50000, 40, 1021, 1_000_003, 999_983
+    vocab, H, buckets, mp, mc = 50000, 40, 2039, 1_000_003, 999_983
     g = torch.Generator().manual_seed(2)
     table = torch.randn(buckets + 1, H, generator=g).to(dtype)
     sg, sp = torch.zeros(4, 1, dtype=torch.int32, device=DEV), torch.zeros(4, 1, dtype=torch.int32)
@@ -231,7 +231,7 @@ def test_bigram_rows_and_the_token_before_a_step(cuda_kernels, dtype):
 # ------------------------------------------------------------------ convolution with its options
 
 @pytest.mark.parametrize("dtype,tol", [(torch.float32, 3e-6), (torch.bfloat16, 1.5e-2)])
-@pytest.mark.parametrize("taps,C,col0,width", [(3, 64, 0, 64), (4, 80, 32, 120), (2, 37, 5, 50), (1, 16, 0, 16), (5, 24, 8, 40), (4, 448, 256, 712)])
+@pytest.mark.parametrize("taps,C,col0,width", [(3, 64, 0, 64), (4, 80, 32, 120), (2, 37, 5, 50), (1, 16, 0, 16), (5, 24, 8, 40), (4, 384, 128, 600)])
 def test_convolution_alone_with_bias_activation_and_column_slices(cuda_kernels, dtype, tol, taps, C, col0, width):
     plain = PlainKernels(wide=True)
     g = torch.Generator().manual_seed(taps * 100 + C)
@@ -256,7 +256,7 @@ def test_convolution_alone_with_bias_activation_and_column_slices(cuda_kernels, 
 
 # ------------------------------------------------------------------ sigmoid routing, plain gated experts
 
-@pytest.mark.parametrize("n,top", [(5, 1), (20, 3), (7, 7), (300, 8), (1, 1), (2, 2), (12, 4)])
+@pytest.mark.parametrize("n,top", [(5, 1), (20, 3), (7, 7), (300, 8), (1, 1), (2, 2), (14, 5)])
 def test_router_sigmoid_scores_over_the_chosen_sum(cuda_kernels, n, top):
     plain = PlainKernels(wide=True)
     z = 3.0 * torch.randn(33, n, generator=torch.Generator().manual_seed(n * 10 + top))
@@ -270,7 +270,7 @@ def test_router_sigmoid_scores_over_the_chosen_sum(cuda_kernels, n, top):
 
 
 @pytest.mark.parametrize("dtype,tol", [(torch.float32, 1e-5), (torch.bfloat16, 2e-2)])
-@pytest.mark.parametrize("T,width,ff,experts,top", [(5, 64, 40, 5, 2), (1, 48, 24, 1, 1), (33, 96, 16, 7, 7), (9, 256, 64, 12, 4)])
+@pytest.mark.parametrize("T,width,ff,experts,top", [(5, 64, 40, 5, 2), (1, 48, 24, 1, 1), (33, 96, 16, 7, 7), (9, 192, 56, 10, 3)])
 def test_plain_gated_experts_few_tokens(cuda_kernels, dtype, tol, T, width, ff, experts, top):
     plain = PlainKernels(wide=True)
     g = torch.Generator().manual_seed(T + width)
@@ -336,7 +336,7 @@ def _step_ctx(kernels, dtype, cache, spans, device):
 
 @pytest.mark.parametrize("dtype,tol", [(torch.float32, 1e-4), (torch.bfloat16, 3e-2)])
 @pytest.mark.parametrize("nq,nkv,d,dv,page,window,rot,q_temp", [
-    (4, 2, 16, 8, 8, 21, 8, None), (2, 1, 64, 32, 16, 136, 32, None), (3, 3, 12, 12, 4, 7, 12, None), (4, 2, 64, 64, 16, None, 0, (0.3, 128)),
+    (4, 2, 16, 8, 8, 21, 8, None), (2, 1, 64, 32, 16, 150, 16, None), (3, 3, 12, 12, 4, 7, 12, None), (4, 2, 64, 64, 16, None, 0, (0.3, 128)),
     (2, 2, 24, 48, 16, 16, 0, (1.5, 9)), (8, 4, 64, 64, 16, 100, 32, None)])
 def test_attention_planted_keys_window_edges_sink_and_far_keys(cuda_kernels, dtype, tol, nq, nkv, d, dv, page, window, rot, q_temp):
     """A prompt of 300 tokens and then 40 decoded ones.  For sixteen queries one key is planted (a large product with that
